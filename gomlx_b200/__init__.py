@@ -1,0 +1,17 @@
+"""gomlx_b200: B200-native GGML block-quantized dense (Q8_0, Q4_0, Q4_K, Q6_K) behind the
+quantized Dense / Gather API of gomlx/gomlx.  All compute lives in libb200q.so (hand-written
+sm_100a CUDA behind the C ABI of include/b200q.h); this package is the thin host layer."""
+from . import _native
+from ._native import B200QError, NotImplementedByBackend
+from .activation import ActivationType, Type as Activation
+from .ggml import GGMLQuantType, can_decompose, logical_k, row_bytes
+from .nn import (Quantization, QuantizationScheme, ResidentWeight, backend_fused_quantized_dense,
+                 backend_quantized_embedding_lookup, dequantize, last_kernel, quantized_dense, quantized_gather,
+                 resident, shard_rows, upload)
+
+__all__ = [
+    "Activation", "ActivationType", "B200QError", "GGMLQuantType", "NotImplementedByBackend", "Quantization",
+    "QuantizationScheme", "ResidentWeight", "backend_fused_quantized_dense", "backend_quantized_embedding_lookup",
+    "can_decompose", "dequantize", "last_kernel", "logical_k", "quantized_dense", "quantized_gather", "resident",
+    "row_bytes", "shard_rows", "upload",
+]

@@ -1,0 +1,85 @@
+"""ctypes binding of libb200q.so (declarations mirror include/b200q.h).
+
+There is no CPU fallback: if the shared library is missing or fails to load, importing
+the compute entry points raises immediately.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+from .build import LIB_PATH
+
+OK, EINVAL, ENOTIMPL, ECUDA, ENOMEM, ETIMEOUT, EHANDLE = 0, -1, -2, -3, -4, -5, -6
+F32, BF16 = 0, 1
+KERNEL_NONE, KERNEL_GEMV_MMA, KERNEL_GEMM_TCGEN05 = 0, 1, 2
+
+# Every symbol include/b200q.h declares: name -> (restype, argtypes)
+_i, _i64, _vp, _sz = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p, ctypes.c_size_t
+_u64 = ctypes.c_uint64
+_pi, _pi64, _pu64 = ctypes.POINTER(_i), ctypes.POINTER(_i64), ctypes.POINTER(_u64)
+SYMBOLS = {
+    "b200q_version": (_i, []),
+    "b200q_last_error": (ctypes.c_char_p, []),
+    "b200q_device_count": (_i, [_pi]),
+    "b200q_ggml_bytes_per_block": (_i, [_i]),
+    "b200q_ggml_values_per_block": (_i, [_i]),
+    "b200q_ggml_type_name": (ctypes.c_char_p, [_i]),
+    "b200q_ggml_can_decompose": (_i, [_i]),
+    "b200q_shard_rows": (_i, [_i64, _i, _i, _pi64, _pi64]),
+    "b200q_weight_upload": (_i, [_i, _i, _i64, _i64, _vp, _i64, _i, _pu64]),
+    "b200q_weight_free": (_i, [_u64]),
+    "b200q_weight_info": (_i, [_u64, _pi, _pi64, _pi64, _pi, _pi64]),
+    "b200q_weight_live_count": (_i, []),
+    "b200q_dequantize": (_i, [_u64, _vp, _vp]),
+    "b200q_dense": (_i, [_u64, _vp, _i, _i64, _vp, _i, _vp, _i64, _vp]),
+    "b200q_embedding_lookup": (_i, [_u64, _vp, _i64, _vp, _vp]),
+    "b200q_last_kernel": (_i, []),
+    "b200q_dense_host": (_i, [_u64, _vp, _i, _i64, _vp, _i, _vp]),
+    "b200q_embedding_lookup_host": (_i, [_u64, _vp, _i64, _vp]),
+    "b200q_dequantize_host": (_i, [_u64, _vp]),
+    "b200q_buffer_alloc": (_i, [_i, _sz, ctypes.POINTER(_vp)]),
+    "b200q_buffer_free": (_i, [_i, _vp]),
+    "b200q_buffer_h2d": (_i, [_i, _vp, _vp, _sz, _vp]),
+    "b200q_buffer_d2h": (_i, [_i, _vp, _vp, _sz, _vp]),
+    "b200q_stream_sync": (_i, [_i, _vp]),
+}
+
+
+class B200QError(RuntimeError):
+    """A b200q call returned a negative status."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"b200q error {code}: {message}")
+        self.code = code
+
+
+class NotImplementedByBackend(B200QError):
+    """Status B200Q_ENOTIMPL: the counterpart of compute.ErrNotImplemented
+    (core/graph/fused_ops.go:357), on which callers fall back to a decomposed graph."""
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Loads libb200q.so; raises (never falls back) when it is absent."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m gomlx_b200.build` (nvcc, sm_100a). "
+                "gomlx_b200 has no CPU or PyTorch fallback.")
+        L = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = L
+    return _lib
+
+
+def check(code: int) -> int:
+    if code < 0:
+        msg = lib().b200q_last_error().decode("utf-8", "replace")
+        raise (NotImplementedByBackend if code == ENOTIMPL else B200QError)(code, msg)
+    return code

@@ -1,0 +1,320 @@
+// C ABI of the b200q library: weight residency, dispatch, host-buffer entry points.
+// The reference interfaces each function stands behind are cited in include/b200q.h.
+#include "common.cuh"
+
+#include <atomic>
+#include <memory>
+#include <mutex>
+#include <unordered_map>
+
+namespace b200q {
+
+static thread_local std::string g_error;
+static thread_local int g_last_kernel = B200Q_KERNEL_NONE;
+
+void set_error(const std::string &msg) { g_error = msg; }
+int fail(int code, const std::string &msg) {
+    g_error = msg;
+    return code;
+}
+int cuda_fail(cudaError_t e, const char *what) {
+    g_error = std::string(what) + ": " + cudaGetErrorString(e);
+    return e == cudaErrorMemoryAllocation ? B200Q_ENOMEM : B200Q_ECUDA;
+}
+
+namespace {
+
+std::mutex g_mu;
+std::unordered_map<uint64_t, std::shared_ptr<Weight>> g_weights;
+std::atomic<uint64_t> g_next{1};
+
+std::shared_ptr<Weight> find(b200q_weight_t h) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_weights.find(h);
+    return it == g_weights.end() ? nullptr : it->second;
+}
+
+bool supported(int t) { return t == kQ4_0 || t == kQ8_0 || t == kQ4_K || t == kQ6_K; }
+
+// Pops the status word written by the gather kernel.
+int check_gather_status(const Weight &w, cudaStream_t s) {
+    int st = 0;
+    B200Q_CUDA(cudaMemcpyAsync(&st, w.status, sizeof(int), cudaMemcpyDeviceToHost, s));
+    B200Q_CUDA(cudaStreamSynchronize(s));
+    if (st != 0) {
+        B200Q_CUDA(cudaMemsetAsync(w.status, 0, sizeof(int), s));
+        return fail(B200Q_EINVAL, "embedding_lookup: index out of range");
+    }
+    return B200Q_OK;
+}
+
+}  // namespace
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+int b200q_version(void) { return 100; }
+
+const char *b200q_last_error(void) { return g_error.c_str(); }
+
+int b200q_device_count(int *count) {
+    if (!count) return fail(B200Q_EINVAL, "device_count: null output");
+    B200Q_CUDA(cudaGetDeviceCount(count));
+    return B200Q_OK;
+}
+
+int b200q_ggml_bytes_per_block(int t) { return fmt_bpb(t); }
+int b200q_ggml_values_per_block(int t) { return fmt_vpb(t); }
+const char *b200q_ggml_type_name(int t) {
+    switch (t) {
+    case kQ4_0: return "Q4_0";
+    case kQ8_0: return "Q8_0";
+    case kQ4_K: return "Q4_K";
+    case kQ6_K: return "Q6_K";
+    case kIQ4_NL: return "IQ4_NL";
+    }
+    return nullptr;
+}
+int b200q_ggml_can_decompose(int t) { return t == kQ4_0 || t == kQ8_0 || t == kIQ4_NL; }
+
+int b200q_shard_rows(int64_t n_rows, int rank, int world, int64_t *row_begin, int64_t *row_count) {
+    if (n_rows < 0 || world < 1 || rank < 0 || rank >= world || !row_begin || !row_count)
+        return fail(B200Q_EINVAL, "shard_rows: bad arguments");
+    const int64_t tiles = (n_rows + 15) / 16;
+    const int64_t base = tiles / world, extra = tiles % world;
+    const int64_t t0 = rank * base + (rank < extra ? rank : extra);
+    const int64_t tn = base + (rank < extra ? 1 : 0);
+    int64_t b = t0 * 16, e = (t0 + tn) * 16;
+    if (b > n_rows) b = n_rows;
+    if (e > n_rows) e = n_rows;
+    *row_begin = b;
+    *row_count = e - b;
+    return B200Q_OK;
+}
+
+int b200q_weight_upload(int device, int ggml_type, int64_t n_rows, int64_t k, const void *bytes, int64_t nbytes,
+                        int src_on_device, b200q_weight_t *out) {
+    if (!out) return fail(B200Q_EINVAL, "weight_upload: null output handle");
+    *out = 0;
+    if (ggml_type == kIQ4_NL)
+        return fail(B200Q_ENOTIMPL, "weight_upload: IQ4_NL is not implemented (lookup table not available)");
+    if (!supported(ggml_type)) return fail(B200Q_ENOTIMPL, "weight_upload: unsupported GGML type");
+    const int vpb = fmt_vpb(ggml_type), bpb = fmt_bpb(ggml_type);
+    if (n_rows <= 0 || k <= 0) return fail(B200Q_EINVAL, "weight_upload: empty weight");
+    if (k % vpb) return fail(B200Q_EINVAL, "weight_upload: K is not a multiple of the block size");
+    if (nbytes != n_rows * (k / vpb) * bpb) return fail(B200Q_EINVAL, "weight_upload: nbytes does not match [N, K]");
+    if (!bytes) return fail(B200Q_EINVAL, "weight_upload: null data");
+    if (n_rows > (int64_t)1 << 31 || k > (int64_t)1 << 30) return fail(B200Q_EINVAL, "weight_upload: weight too large");
+    B200Q_CUDA(cudaSetDevice(device));
+
+    auto w = std::make_shared<Weight>();
+    w->type = ggml_type, w->device = device, w->n = n_rows, w->k = k;
+    const int tk = fmt_tk(ggml_type);
+    w->rt = (n_rows + 15) / 16;
+    w->kt = (k + tk - 1) / tk;
+    w->bytes = w->rt * w->kt * (int64_t)fmt_tile_bytes(ggml_type);
+    B200Q_CUDA(cudaMalloc(&w->tiles, (size_t)w->bytes));
+    cudaError_t e = cudaMalloc(&w->status, sizeof(int));
+    if (e != cudaSuccess) {
+        cudaFree(w->tiles);
+        return cuda_fail(e, "cudaMalloc(status)");
+    }
+    const uint8_t *src = static_cast<const uint8_t *>(bytes);
+    uint8_t *staging = nullptr;
+    int rc = B200Q_OK;
+    do {
+        if (!src_on_device) {
+            if ((e = cudaMalloc(&staging, (size_t)nbytes)) != cudaSuccess) { rc = cuda_fail(e, "cudaMalloc(staging)"); break; }
+            if ((e = cudaMemcpy(staging, bytes, (size_t)nbytes, cudaMemcpyHostToDevice)) != cudaSuccess) { rc = cuda_fail(e, "cudaMemcpy(H2D weights)"); break; }
+            src = staging;
+        }
+        if ((e = cudaMemsetAsync(w->status, 0, sizeof(int), 0)) != cudaSuccess) { rc = cuda_fail(e, "cudaMemset(status)"); break; }
+        if ((rc = launch_repack(*w, src, 0)) != 0) break;
+        if ((e = cudaStreamSynchronize(0)) != cudaSuccess) { rc = cuda_fail(e, "repack"); break; }
+    } while (0);
+    if (staging) cudaFree(staging);
+    if (rc != 0) {
+        cudaFree(w->tiles);
+        cudaFree(w->status);
+        return rc;
+    }
+    const uint64_t h = g_next.fetch_add(1);
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        g_weights[h] = w;
+    }
+    *out = h;
+    return B200Q_OK;
+}
+
+int b200q_weight_free(b200q_weight_t h) {
+    std::shared_ptr<Weight> w;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        auto it = g_weights.find(h);
+        if (it == g_weights.end()) return fail(B200Q_EHANDLE, "weight_free: unknown handle");
+        w = it->second;
+        g_weights.erase(it);
+    }
+    B200Q_CUDA(cudaSetDevice(w->device));
+    B200Q_CUDA(cudaFree(w->tiles));
+    B200Q_CUDA(cudaFree(w->status));
+    return B200Q_OK;
+}
+
+int b200q_weight_info(b200q_weight_t h, int *ggml_type, int64_t *n_rows, int64_t *k, int *device,
+                      int64_t *device_bytes) {
+    auto w = find(h);
+    if (!w) return fail(B200Q_EHANDLE, "weight_info: unknown handle");
+    if (ggml_type) *ggml_type = w->type;
+    if (n_rows) *n_rows = w->n;
+    if (k) *k = w->k;
+    if (device) *device = w->device;
+    if (device_bytes) *device_bytes = w->bytes;
+    return B200Q_OK;
+}
+
+int b200q_weight_live_count(void) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    return (int)g_weights.size();
+}
+
+int b200q_dequantize(b200q_weight_t h, float *out_dev, void *stream) {
+    auto w = find(h);
+    if (!w) return fail(B200Q_EHANDLE, "dequantize: unknown handle");
+    if (!out_dev) return fail(B200Q_EINVAL, "dequantize: null output");
+    B200Q_CUDA(cudaSetDevice(w->device));
+    return launch_dequantize(*w, out_dev, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_dense(b200q_weight_t h, const void *x_dev, int x_dtype, int64_t m, const float *bias_dev, int activation,
+                float *y_dev, int64_t y_ld, void *stream) {
+    auto w = find(h);
+    if (!w) return fail(B200Q_EHANDLE, "dense: unknown handle");
+    if (!x_dev || !y_dev) return fail(B200Q_EINVAL, "dense: null x or y");
+    if (x_dtype != B200Q_F32 && x_dtype != B200Q_BF16) return fail(B200Q_EINVAL, "dense: x dtype must be f32 or bf16");
+    if (activation < B200Q_ACT_NONE || activation > B200Q_ACT_TANH) return fail(B200Q_EINVAL, "dense: bad activation");
+    if (m < 0) return fail(B200Q_EINVAL, "dense: negative m");
+    if (y_ld == 0) y_ld = w->n;
+    if (y_ld < w->n) return fail(B200Q_EINVAL, "dense: y_ld smaller than N");
+    if (reinterpret_cast<uintptr_t>(x_dev) & 15) return fail(B200Q_EINVAL, "dense: x must be 16-byte aligned");
+    if (m == 0) return B200Q_OK;
+    B200Q_CUDA(cudaSetDevice(w->device));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (m <= 16) {
+        g_last_kernel = B200Q_KERNEL_GEMV_MMA;
+        return launch_gemv(*w, x_dev, x_dtype, (int)m, bias_dev, activation, y_dev, y_ld, s);
+    }
+    g_last_kernel = B200Q_KERNEL_GEMM_TCGEN05;
+    return launch_gemm(*w, x_dev, x_dtype, m, bias_dev, activation, y_dev, y_ld, s);
+}
+
+int b200q_embedding_lookup(b200q_weight_t h, const int32_t *idx_dev, int64_t n_idx, float *out_dev, void *stream) {
+    auto w = find(h);
+    if (!w) return fail(B200Q_EHANDLE, "embedding_lookup: unknown handle");
+    if (n_idx < 0) return fail(B200Q_EINVAL, "embedding_lookup: negative count");
+    if (n_idx == 0) return B200Q_OK;
+    if (!idx_dev || !out_dev) return fail(B200Q_EINVAL, "embedding_lookup: null pointer");
+    B200Q_CUDA(cudaSetDevice(w->device));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int rc = launch_gather(*w, idx_dev, n_idx, out_dev, s);
+    if (rc != 0) return rc;
+    return check_gather_status(*w, s);
+}
+
+int b200q_last_kernel(void) { return g_last_kernel; }
+
+int b200q_dense_host(b200q_weight_t h, const void *x_host, int x_dtype, int64_t m, const float *bias_host,
+                     int activation, float *y_host) {
+    auto w = find(h);
+    if (!w) return fail(B200Q_EHANDLE, "dense_host: unknown handle");
+    if (m < 0 || !x_host || !y_host) return fail(B200Q_EINVAL, "dense_host: bad arguments");
+    if (m == 0) return B200Q_OK;
+    if (x_dtype != B200Q_F32 && x_dtype != B200Q_BF16) return fail(B200Q_EINVAL, "dense_host: x dtype must be f32 or bf16");
+    B200Q_CUDA(cudaSetDevice(w->device));
+    const size_t xb = (size_t)m * w->k * (x_dtype == B200Q_F32 ? 4 : 2), yb = (size_t)m * w->n * 4, bb = (size_t)w->n * 4;
+    uint8_t *dev = nullptr;
+    const size_t xo = 0, yo = (xb + 255) & ~(size_t)255, bo = yo + ((yb + 255) & ~(size_t)255);
+    B200Q_CUDA(cudaMalloc(&dev, bo + bb));
+    int rc = B200Q_OK;
+    cudaError_t e;
+    do {
+        if ((e = cudaMemcpyAsync(dev + xo, x_host, xb, cudaMemcpyHostToDevice, 0)) != cudaSuccess) { rc = cuda_fail(e, "H2D x"); break; }
+        if (bias_host && (e = cudaMemcpyAsync(dev + bo, bias_host, bb, cudaMemcpyHostToDevice, 0)) != cudaSuccess) { rc = cuda_fail(e, "H2D bias"); break; }
+        rc = b200q_dense(h, dev + xo, x_dtype, m, bias_host ? reinterpret_cast<float *>(dev + bo) : nullptr, activation,
+                         reinterpret_cast<float *>(dev + yo), 0, nullptr);
+        if (rc != 0) break;
+        if ((e = cudaMemcpyAsync(y_host, dev + yo, yb, cudaMemcpyDeviceToHost, 0)) != cudaSuccess) { rc = cuda_fail(e, "D2H y"); break; }
+        if ((e = cudaStreamSynchronize(0)) != cudaSuccess) { rc = cuda_fail(e, "dense_host sync"); break; }
+    } while (0);
+    cudaFree(dev);
+    return rc;
+}
+
+int b200q_embedding_lookup_host(b200q_weight_t h, const int32_t *idx_host, int64_t n_idx, float *out_host) {
+    auto w = find(h);
+    if (!w) return fail(B200Q_EHANDLE, "embedding_lookup_host: unknown handle");
+    if (n_idx < 0) return fail(B200Q_EINVAL, "embedding_lookup_host: negative count");
+    if (n_idx == 0) return B200Q_OK;
+    if (!idx_host || !out_host) return fail(B200Q_EINVAL, "embedding_lookup_host: null pointer");
+    B200Q_CUDA(cudaSetDevice(w->device));
+    const size_t ib = ((size_t)n_idx * 4 + 255) & ~(size_t)255, ob = (size_t)n_idx * w->k * 4;
+    uint8_t *dev = nullptr;
+    B200Q_CUDA(cudaMalloc(&dev, ib + ob));
+    int rc = B200Q_OK;
+    cudaError_t e;
+    do {
+        if ((e = cudaMemcpyAsync(dev, idx_host, (size_t)n_idx * 4, cudaMemcpyHostToDevice, 0)) != cudaSuccess) { rc = cuda_fail(e, "H2D idx"); break; }
+        rc = b200q_embedding_lookup(h, reinterpret_cast<int32_t *>(dev), n_idx, reinterpret_cast<float *>(dev + ib), nullptr);
+        if (rc != 0) break;
+        if ((e = cudaMemcpy(out_host, dev + ib, ob, cudaMemcpyDeviceToHost)) != cudaSuccess) { rc = cuda_fail(e, "D2H rows"); break; }
+    } while (0);
+    cudaFree(dev);
+    return rc;
+}
+
+int b200q_dequantize_host(b200q_weight_t h, float *out_host) {
+    auto w = find(h);
+    if (!w) return fail(B200Q_EHANDLE, "dequantize_host: unknown handle");
+    if (!out_host) return fail(B200Q_EINVAL, "dequantize_host: null output");
+    B200Q_CUDA(cudaSetDevice(w->device));
+    float *dev = nullptr;
+    const size_t ob = (size_t)w->n * w->k * 4;
+    B200Q_CUDA(cudaMalloc(&dev, ob));
+    int rc = launch_dequantize(*w, dev, 0);
+    cudaError_t e;
+    if (rc == 0 && (e = cudaMemcpy(out_host, dev, ob, cudaMemcpyDeviceToHost)) != cudaSuccess) rc = cuda_fail(e, "D2H dequantized");
+    cudaFree(dev);
+    return rc;
+}
+
+int b200q_buffer_alloc(int device, size_t nbytes, void **dev_ptr) {
+    if (!dev_ptr) return fail(B200Q_EINVAL, "buffer_alloc: null output");
+    B200Q_CUDA(cudaSetDevice(device));
+    B200Q_CUDA(cudaMalloc(dev_ptr, nbytes ? nbytes : 1));
+    return B200Q_OK;
+}
+int b200q_buffer_free(int device, void *dev_ptr) {
+    B200Q_CUDA(cudaSetDevice(device));
+    B200Q_CUDA(cudaFree(dev_ptr));
+    return B200Q_OK;
+}
+int b200q_buffer_h2d(int device, void *dst_dev, const void *src_host, size_t nbytes, void *stream) {
+    B200Q_CUDA(cudaSetDevice(device));
+    B200Q_CUDA(cudaMemcpyAsync(dst_dev, src_host, nbytes, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+    return B200Q_OK;
+}
+int b200q_buffer_d2h(int device, void *dst_host, const void *src_dev, size_t nbytes, void *stream) {
+    B200Q_CUDA(cudaSetDevice(device));
+    B200Q_CUDA(cudaMemcpyAsync(dst_host, src_dev, nbytes, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+    return B200Q_OK;
+}
+int b200q_stream_sync(int device, void *stream) {
+    B200Q_CUDA(cudaSetDevice(device));
+    B200Q_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    return B200Q_OK;
+}
+
+}  // extern "C"

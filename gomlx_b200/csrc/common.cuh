@@ -1,0 +1,61 @@
+// Shared declarations of the b200q library (internal; the public surface is include/b200q.h).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <string>
+
+#include "../../include/b200q.h"
+#include "layout.cuh"
+
+namespace b200q {
+
+// One resident weight matrix (a shard, when the caller uploaded a row range).
+struct Weight {
+    int type = 0;
+    int device = 0;
+    int64_t n = 0, k = 0;        // logical rows / values per row
+    int64_t rt = 0, kt = 0;      // row tiles (16 rows) and k tiles (TK values)
+    uint8_t *tiles = nullptr;    // rt * kt * TILE bytes in lane-tile order
+    int64_t bytes = 0;
+    int *status = nullptr;       // device status word (embedding index check)
+};
+
+void set_error(const std::string &msg);
+int fail(int code, const std::string &msg);
+int cuda_fail(cudaError_t e, const char *what);
+
+#define B200Q_CUDA(call)                                      \
+    do {                                                      \
+        cudaError_t e__ = (call);                             \
+        if (e__ != cudaSuccess) return cuda_fail(e__, #call); \
+    } while (0)
+
+// repack.cu
+int launch_repack(const Weight &w, const uint8_t *src_dev, cudaStream_t s);
+int launch_dequantize(const Weight &w, float *out, cudaStream_t s);
+int launch_gather(const Weight &w, const int32_t *idx, int64_t n_idx, float *out, cudaStream_t s);
+
+// gemv_mma.cu
+int launch_gemv(const Weight &w, const void *x, int x_dtype, int m, const float *bias, int act, float *y, int64_t y_ld,
+                cudaStream_t s);
+
+// gemm_tcgen05.cu
+int launch_gemm(const Weight &w, const void *x, int x_dtype, int64_t m, const float *bias, int act, float *y,
+                int64_t y_ld, cudaStream_t s);
+
+// Fused epilogue: compute.ActivationType semantics (ml/layers/activation/activation.go:91-121,195-244).
+__device__ __forceinline__ float apply_activation(int act, float v) {
+    switch (act) {
+    case B200Q_ACT_RELU: return fmaxf(v, 0.0f);
+    case B200Q_ACT_SILU: return v * (1.0f / (1.0f + expf(-v)));
+    case B200Q_ACT_GELU: return v * ((erff(v / 1.41421356237309504880f) + 1.0f) * 0.5f);
+    case B200Q_ACT_HARDSWISH: return v * fminf(fmaxf(v * (1.0f / 6.0f) + 0.5f, 0.0f), 1.0f);
+    case B200Q_ACT_TANH: return tanhf(v);
+    default: return v;
+    }
+}
+
+}  // namespace b200q

@@ -1,0 +1,284 @@
+"""Host-side mirror of the reference's quantized dense / gather API over the b200q C ABI.
+
+Names, argument meaning and error behaviour follow gomlx/gomlx:
+
+  Quantization                       core/graph/fused_ops.go:18-48
+  backend_fused_quantized_dense      core/graph/fused_ops.go:195-245
+  backend_quantized_embedding_lookup core/graph/fused_ops.go:281-309
+  quantized_dense                    ml/nn/quantized_dense.go:31-71
+  quantized_gather                   ml/nn/quantized_gather.go:30-43
+  upload / ResidentWeight            core/tensors/ondevice.go:59-71,285-295 (upload once, never donated)
+
+Device memory and streams come from PyTorch (``tensor.data_ptr()``, the current CUDA stream); all
+arithmetic runs in libb200q.so.  numpy inputs take the host-buffer entry points, which copy inside.
+"""
+from __future__ import annotations
+
+import ctypes
+import dataclasses
+import enum
+import threading
+import weakref
+from typing import Optional, Tuple, Union
+
+import numpy as np
+
+from . import _native as nat
+from .activation import ActivationType, Type as Activation
+from .ggml import GGMLQuantType, can_decompose, logical_k
+
+try:  # plumbing only
+    import torch
+except ImportError:  # pragma: no cover
+    torch = None
+
+
+class QuantizationScheme(enum.IntEnum):
+    """compute.QuantizationScheme."""
+
+    LINEAR = 0
+    NF4 = 1
+    GGML = 2
+
+
+@dataclasses.dataclass
+class Quantization:
+    """graph.Quantization (core/graph/fused_ops.go:18-48).  For GGML only ``scheme`` and
+    ``ggml_type`` are used: scales live inside the blocks."""
+
+    scheme: QuantizationScheme
+    ggml_type: Optional[GGMLQuantType] = None
+    scale: object = None
+    zero_point: object = None
+    block_axis: int = 0
+    block_size: int = 0
+
+
+class ResidentWeight:
+    """Packed GGML weight kept on one device: uploaded once, reused by every call, released by
+    ``free()`` or garbage collection (Tensor.Buffer / Buffer.Finalize semantics)."""
+
+    def __init__(self, handle: int, ggml_type: GGMLQuantType, n: int, k: int, device: int,
+                 row_begin: int = 0, n_total: Optional[int] = None):
+        self.handle, self.ggml_type, self.n, self.k, self.device = handle, ggml_type, n, k, device
+        self.row_begin, self.n_total = row_begin, n if n_total is None else n_total
+        self._finalizer = weakref.finalize(self, _free_handle, handle)
+
+    @property
+    def device_bytes(self) -> int:
+        out = ctypes.c_int64()
+        nat.check(nat.lib().b200q_weight_info(self.handle, None, None, None, None, ctypes.byref(out)))
+        return out.value
+
+    def free(self) -> None:
+        if self._finalizer.alive:
+            self._finalizer.detach()
+            nat.check(nat.lib().b200q_weight_free(self.handle))
+            self.handle = 0
+
+
+def _free_handle(handle: int) -> None:
+    try:
+        nat.lib().b200q_weight_free(handle)
+    except Exception:  # interpreter shutdown
+        pass
+
+
+def shard_rows(n_rows: int, rank: int, world: int) -> Tuple[int, int]:
+    """Row range [begin, begin+count) of shard ``rank`` when the N output features are split."""
+    b, c = ctypes.c_int64(), ctypes.c_int64()
+    nat.check(nat.lib().b200q_shard_rows(n_rows, rank, world, ctypes.byref(b), ctypes.byref(c)))
+    return b.value, c.value
+
+
+def upload(weights, ggml_type: GGMLQuantType, device: int = 0, shard: Optional[Tuple[int, int]] = None
+           ) -> ResidentWeight:
+    """Copies a packed ``[N, bytesPerRow]`` uint8 weight (numpy, or torch on cpu / cuda) to ``device``
+    once.  ``shard=(rank, world)`` keeps only this rank's contiguous block of output rows."""
+    ggml_type = GGMLQuantType(ggml_type)
+    is_torch = torch is not None and isinstance(weights, torch.Tensor)
+    if is_torch:
+        if weights.dtype != torch.uint8 or weights.dim() != 2:
+            raise ValueError("weights must be a [N, bytesPerRow] uint8 tensor")
+        weights = weights.contiguous()
+        n_total, bpr = weights.shape
+    else:
+        weights = np.ascontiguousarray(weights)
+        if weights.dtype != np.uint8 or weights.ndim != 2:
+            raise ValueError("weights must be a [N, bytesPerRow] uint8 array")
+        n_total, bpr = weights.shape
+    k = logical_k(ggml_type, bpr)
+    begin, count = (0, n_total) if shard is None else shard_rows(n_total, *shard)
+    part = weights[begin:begin + count]
+    on_device = bool(is_torch and part.is_cuda)
+    if on_device and part.device.index != device:
+        raise ValueError("weights live on a different CUDA device than requested")
+    ptr = part.data_ptr() if is_torch else part.ctypes.data
+    handle = ctypes.c_uint64()
+    nat.check(nat.lib().b200q_weight_upload(device, int(ggml_type), count, k, ctypes.c_void_p(ptr), count * bpr,
+                                            int(on_device), ctypes.byref(handle)))
+    return ResidentWeight(handle.value, ggml_type, count, k, device, begin, n_total)
+
+
+# One upload per (host buffer identity, device): core/tensors/ondevice.go:59-71.  Keyed on identity,
+# never on content, and dropped when the buffer is collected.
+_cache_lock = threading.Lock()
+_cache: dict = {}
+
+
+def resident(weights, quant: Quantization, device: int = 0) -> ResidentWeight:
+    """Returns the device copy of ``weights``, uploading on first use."""
+    if isinstance(weights, ResidentWeight):
+        return weights
+    key = (id(weights), device, int(quant.ggml_type))
+    with _cache_lock:
+        hit = _cache.get(key)
+        if hit is not None:
+            return hit
+    w = upload(weights, quant.ggml_type, device)
+    with _cache_lock:
+        _cache[key] = w
+    try:
+        weakref.finalize(weights, _evict, key)
+    except TypeError:
+        pass
+    return w
+
+
+def _evict(key) -> None:
+    with _cache_lock:
+        w = _cache.pop(key, None)
+    if w is not None:
+        w.free()
+
+
+def _stream_ptr(device: int) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _check_ggml(quant: Optional[Quantization], who: str) -> GGMLQuantType:
+    if quant is None:
+        raise ValueError(f"{who}: quantization must not be None")  # fused_ops.go:198-200
+    if quant.scheme != QuantizationScheme.GGML:
+        if quant.scale is None:
+            raise ValueError(f"{who}: scale must not be None for scheme {quant.scheme.name}")  # :201-203
+        raise nat.NotImplementedByBackend(nat.ENOTIMPL, f"{who}: scheme {quant.scheme.name} is not implemented; "
+                                                        "only QuantGGML runs on this backend")
+    if quant.ggml_type is None:
+        raise ValueError(f"{who}: GGML scheme needs ggml_type")
+    return GGMLQuantType(quant.ggml_type)
+
+
+def backend_fused_quantized_dense(x, weights, bias, wq: Quantization,
+                                  activation: ActivationType = ActivationType.NONE, out=None):
+    """BackendFusedQuantizedDense (core/graph/fused_ops.go:195-245):
+    ``act(x @ dequant(weights)^T + bias)`` with x ``[batch..., K]``, weights ``[N, bytesPerRow]``
+    uint8 (or a ResidentWeight), bias ``[N]`` or None.  Returns ``[batch..., N]`` float32.
+
+    torch CUDA ``x`` -> result is a torch CUDA tensor computed on the current stream;
+    numpy ``x`` -> host-buffer entry point, result is numpy."""
+    _check_ggml(wq, "BackendFusedQuantizedDense")
+    L = nat.lib()
+    if torch is not None and isinstance(x, torch.Tensor):
+        if not x.is_cuda:
+            raise ValueError("torch activations must live on a CUDA device (pass numpy for host buffers)")
+        dev = x.device.index
+        w = resident(weights, wq, dev)
+        if x.dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError("x must be float32 or bfloat16")  # quantized_dense.go:21
+        if x.shape[-1] != w.k:
+            raise ValueError(f"x is shaped {tuple(x.shape)} but the weights have K={w.k}")  # dense.go:39-42
+        x2 = x.reshape(-1, w.k).contiguous()
+        m = x2.shape[0]
+        b = None
+        if bias is not None:
+            b = bias.to(device=x.device, dtype=torch.float32).contiguous()
+            if b.shape != (w.n,):
+                raise ValueError(f"bias must be shaped [{w.n}]")
+        y = out if out is not None else torch.empty((m, w.n), device=x.device, dtype=torch.float32)
+        nat.check(L.b200q_dense(w.handle, ctypes.c_void_p(x2.data_ptr()), nat.F32 if x.dtype == torch.float32 else nat.BF16,
+                                m, ctypes.c_void_p(b.data_ptr()) if b is not None else None, int(activation),
+                                ctypes.c_void_p(y.data_ptr()), y.stride(0) if m > 0 else 0, _stream_ptr(dev)))
+        return y.reshape(*x.shape[:-1], w.n) if out is None else y
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    w = resident(weights, wq, 0)
+    if x.shape[-1] != w.k:
+        raise ValueError(f"x is shaped {x.shape} but the weights have K={w.k}")
+    x2 = x.reshape(-1, w.k)
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    if b is not None and b.shape != (w.n,):
+        raise ValueError(f"bias must be shaped [{w.n}]")
+    y = np.empty((x2.shape[0], w.n), np.float32)
+    nat.check(L.b200q_dense_host(w.handle, x2.ctypes.data_as(ctypes.c_void_p), nat.F32, x2.shape[0],
+                                 b.ctypes.data_as(ctypes.c_void_p) if b is not None else None, int(activation),
+                                 y.ctypes.data_as(ctypes.c_void_p)))
+    return y.reshape(*x.shape[:-1], w.n)
+
+
+def quantized_dense(x, weights, quant: Quantization, bias=None, *optional_activation: Activation):
+    """nn.QuantizedDense (ml/nn/quantized_dense.go:31-71).  At most one activation may be given;
+    it is translated with ``to_backend`` so types the fused op cannot apply are dropped, as in the
+    reference.  Non-GGML schemes raise NotImplementedByBackend (the caller's decomposed fallback)."""
+    if len(optional_activation) > 1:
+        raise ValueError(f"nn.QuantizedDense() can only take one optional activation, got {optional_activation}")
+    act = optional_activation[0] if optional_activation else Activation.NONE
+    return backend_fused_quantized_dense(x, weights, bias, quant, act.to_backend())
+
+
+def backend_quantized_embedding_lookup(data, indices, tq: Quantization):
+    """BackendQuantizedEmbeddingLookup (core/graph/fused_ops.go:281-309): gathers rows of the packed
+    table and dequantizes only those.  ``indices`` is an integer tensor whose last dimension is 1;
+    the result is ``[batch..., K]`` float32."""
+    _check_ggml(tq, "BackendQuantizedEmbeddingLookup")
+    L = nat.lib()
+    if torch is not None and isinstance(indices, torch.Tensor):
+        if not indices.is_cuda:
+            raise ValueError("torch indices must live on a CUDA device (pass numpy for host buffers)")
+        if indices.shape[-1] != 1:
+            raise ValueError("indices must have last dimension 1")
+        dev = indices.device.index
+        w = resident(data, tq, dev)
+        flat = indices.reshape(-1).to(torch.int32).contiguous()
+        out = torch.empty((flat.numel(), w.k), device=indices.device, dtype=torch.float32)
+        nat.check(L.b200q_embedding_lookup(w.handle, ctypes.c_void_p(flat.data_ptr()), flat.numel(),
+                                           ctypes.c_void_p(out.data_ptr()), _stream_ptr(dev)))
+        return out.reshape(*indices.shape[:-1], w.k)
+    idx = np.ascontiguousarray(indices, dtype=np.int32)
+    if idx.shape[-1] != 1:
+        raise ValueError("indices must have last dimension 1")
+    w = resident(data, tq, 0)
+    flat = idx.reshape(-1)
+    out = np.empty((flat.size, w.k), np.float32)
+    nat.check(L.b200q_embedding_lookup_host(w.handle, flat.ctypes.data_as(ctypes.c_void_p), flat.size,
+                                            out.ctypes.data_as(ctypes.c_void_p)))
+    return out.reshape(*idx.shape[:-1], w.k)
+
+
+def quantized_gather(table, indices, quant: Quantization):
+    """nn.QuantizedGather (ml/nn/quantized_gather.go:30-43); only the GGML scheme is supported."""
+    if quant.scheme != QuantizationScheme.GGML:
+        raise ValueError("nn.QuantizedGather: only QuantGGML scheme is supported")
+    return backend_quantized_embedding_lookup(table, indices, quant)
+
+
+def dequantize(weights, ggml_type: GGMLQuantType, device: int = 0):
+    """ggml.Dequantize (ml/ggml/dequant.go:39-54): ``[N, K]`` float32, bit-exact.  Returns a torch
+    CUDA tensor for a ResidentWeight / torch input and numpy for a numpy input."""
+    L = nat.lib()
+    if isinstance(weights, np.ndarray):
+        w = upload(weights, ggml_type, device)
+        try:
+            out = np.empty((w.n, w.k), np.float32)
+            nat.check(L.b200q_dequantize_host(w.handle, out.ctypes.data_as(ctypes.c_void_p)))
+            return out
+        finally:
+            w.free()
+    w = weights if isinstance(weights, ResidentWeight) else resident(weights, Quantization(QuantizationScheme.GGML, ggml_type), device)
+    out = torch.empty((w.n, w.k), device=f"cuda:{w.device}", dtype=torch.float32)
+    nat.check(L.b200q_dequantize(w.handle, ctypes.c_void_p(out.data_ptr()), _stream_ptr(w.device)))
+    return out
+
+
+def last_kernel() -> int:
+    """Which kernel family the last dense call on this thread used (nat.KERNEL_*)."""
+    return nat.lib().b200q_last_kernel()

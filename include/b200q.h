@@ -1,0 +1,151 @@
+/*
+ * b200q — GGML block-quantized dense for NVIDIA B200 (sm_100a), C ABI.
+ *
+ * This is the boundary a GoMLX backend binds with cgo.  Every entry point below
+ * names the reference (gomlx/gomlx) interface it stands behind.  Conventions:
+ *
+ *   - plain C types only; every function returns a b200q_status (0 = OK, < 0 =
+ *     error) and leaves a message for b200q_last_error() (thread-local);
+ *   - "unsupported" is B200Q_ENOTIMPL, which a Go shim maps to an error for which
+ *     compute.IsNotImplemented(err) is true (core/graph/fused_ops.go:357), so
+ *     InternalFusedOpCaller falls back to the decomposed graph;
+ *   - the caller owns host memory, the library owns device memory behind handles;
+ *   - thread-safe: any thread may call any function, the device is selected per
+ *     call (goroutines migrate between OS threads);
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
+ *   - there is no CPU fallback: without a CUDA device every compute call fails
+ *     with B200Q_ECUDA.
+ */
+#ifndef B200Q_H_
+#define B200Q_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    B200Q_OK = 0,
+    B200Q_EINVAL = -1,   /* bad argument (shape, dtype, null pointer) */
+    B200Q_ENOTIMPL = -2, /* valid request this backend does not implement */
+    B200Q_ECUDA = -3,    /* CUDA runtime / driver error (text in last_error) */
+    B200Q_ENOMEM = -4,   /* device or host allocation failed */
+    B200Q_ETIMEOUT = -5, /* a bounded device-side wait gave up */
+    B200Q_EHANDLE = -6   /* unknown or already freed handle */
+} b200q_status;
+
+/* GGML block formats (compute.GGMLQuantType at ml/ggml/dequant.go:20-27,
+ * ml/nn/quantized_dense.go:44-56).  Numeric values are GGML's own type ids. */
+typedef enum {
+    B200Q_GGML_Q4_0 = 2,
+    B200Q_GGML_Q8_0 = 8,
+    B200Q_GGML_Q4_K = 12,
+    B200Q_GGML_Q6_K = 14,
+    B200Q_GGML_IQ4_NL = 20 /* recognised, B200Q_ENOTIMPL: its table is not in the reference */
+} b200q_ggml_type;
+
+/* compute.ActivationType as produced by activation.Type.ToBackend
+ * (ml/layers/activation/activation.go:58-75). */
+typedef enum {
+    B200Q_ACT_NONE = 0,
+    B200Q_ACT_GELU = 1, /* exact erf form */
+    B200Q_ACT_RELU = 2,
+    B200Q_ACT_SILU = 3,
+    B200Q_ACT_HARDSWISH = 4,
+    B200Q_ACT_TANH = 5
+} b200q_activation;
+
+typedef enum { B200Q_F32 = 0, B200Q_BF16 = 1 } b200q_dtype;
+
+/* Which kernel family b200q_dense used (b200q_last_kernel). */
+typedef enum { B200Q_KERNEL_NONE = 0, B200Q_KERNEL_GEMV_MMA = 1, B200Q_KERNEL_GEMM_TCGEN05 = 2 } b200q_kernel;
+
+typedef uint64_t b200q_weight_t; /* resident packed weight matrix */
+
+/* ---- library ---------------------------------------------------------------- */
+
+int b200q_version(void);
+/* Message of the last failing call on this thread ("" if none). */
+const char *b200q_last_error(void);
+/* Backend.NumDevices (core/tensors/ondevice.go:222). */
+int b200q_device_count(int *count);
+
+/* GGMLQuantType.BytesPerBlock / ValuesPerBlock / String (ml/ggml/dequant.go:41,52,
+ * ml/ggml/gather.go:24-25).  Return 0 / NULL for an unknown type. */
+int b200q_ggml_bytes_per_block(int ggml_type);
+int b200q_ggml_values_per_block(int ggml_type);
+const char *b200q_ggml_type_name(int ggml_type);
+/* ggml.CanDecompose (ml/ggml/dequant.go:20-27): 1 for Q4_0, Q8_0, IQ4_NL. */
+int b200q_ggml_can_decompose(int ggml_type);
+
+/* Contiguous row range of shard `rank` out of `world` when a [N, bytesPerRow]
+ * weight is split by output feature (rows are independent, ml/ggml/dequant.go:31-35).
+ * Ranges are multiples of 16 rows except possibly the last. */
+int b200q_shard_rows(int64_t n_rows, int rank, int world, int64_t *row_begin, int64_t *row_count);
+
+/* ---- weight residency ---------------------------------------------------------
+ * Stands behind Backend.BufferFromFlatData for the packed [N, bytesPerRow] uint8
+ * tensor and the "upload once, never donated" rule of Tensor.Buffer /
+ * model.Exec.setSideParamsSingleDevice (core/tensors/ondevice.go:59-71,285-295,
+ * ml/model/exec.go:160-214).  `bytes` holds n_rows rows in native GGML block
+ * layout; it may be a host pointer (src_on_device = 0) or a device pointer on
+ * `device` (src_on_device = 1).  The bytes are copied once and rearranged on the
+ * device into the kernels' tile order (same bits, same size up to padding); the
+ * source may be released as soon as the call returns.
+ */
+int b200q_weight_upload(int device, int ggml_type, int64_t n_rows, int64_t k, const void *bytes, int64_t nbytes,
+                        int src_on_device, b200q_weight_t *out);
+/* Buffer.Finalize (core/tensors/ondevice.go:130-144). */
+int b200q_weight_free(b200q_weight_t w);
+int b200q_weight_info(b200q_weight_t w, int *ggml_type, int64_t *n_rows, int64_t *k, int *device,
+                      int64_t *device_bytes);
+/* Number of resident weights (leak checks). */
+int b200q_weight_live_count(void);
+
+/* ---- compute (device pointers) -------------------------------------------------- */
+
+/* ggml.Dequantize (ml/ggml/dequant.go:39-54): out_dev[N, K] f32, bit-exact. */
+int b200q_dequantize(b200q_weight_t w, float *out_dev, void *stream);
+
+/* compute.Function.FusedQuantizedDense for Scheme == QuantGGML
+ * (core/graph/fused_ops.go:195-245, ml/nn/quantized_dense.go:31-71):
+ *   y[m, n] = act(sum_k x[m, k] * dequant(W)[n, k] + bias[n])
+ * x: [m, K] row-major, f32 or bf16; bias: [N] f32 or NULL; y: [m, N] f32 (row stride
+ * y_ld elements, y_ld >= N; pass 0 for N).  m <= 16 runs the decode GEMV, larger m
+ * the tcgen05 GEMM. */
+int b200q_dense(b200q_weight_t w, const void *x_dev, int x_dtype, int64_t m, const float *bias_dev, int activation,
+                float *y_dev, int64_t y_ld, void *stream);
+
+/* compute.Function.QuantizedEmbeddingLookup (core/graph/fused_ops.go:281-309,
+ * ml/ggml/gather.go:21-49): out_dev[i, :] = dequant(table[idx[i], :]).  An index
+ * outside [0, N) yields B200Q_EINVAL after the launch completes (checked on the
+ * device, reported through a status word; no fault). */
+int b200q_embedding_lookup(b200q_weight_t table, const int32_t *idx_dev, int64_t n_idx, float *out_dev,
+                           void *stream);
+
+/* Kernel family chosen by the last b200q_dense on this thread. */
+int b200q_last_kernel(void);
+
+/* ---- compute (host pointers; copies inside) ---------------------------------------
+ * The call a Go Executable.Execute makes when activations live in Go memory
+ * (core/graph/graph.go:651-689): H2D of x (and bias), kernel, D2H of y, synchronous. */
+int b200q_dense_host(b200q_weight_t w, const void *x_host, int x_dtype, int64_t m, const float *bias_host,
+                     int activation, float *y_host);
+int b200q_embedding_lookup_host(b200q_weight_t table, const int32_t *idx_host, int64_t n_idx, float *out_host);
+int b200q_dequantize_host(b200q_weight_t w, float *out_host);
+
+/* ---- plumbing ---------------------------------------------------------------------
+ * Backend.BufferFromFlatData / Buffer.ToFlatData / Buffer.Finalize for activation
+ * buffers (core/tensors/ondevice.go:285,462,137). */
+int b200q_buffer_alloc(int device, size_t nbytes, void **dev_ptr);
+int b200q_buffer_free(int device, void *dev_ptr);
+int b200q_buffer_h2d(int device, void *dst_dev, const void *src_host, size_t nbytes, void *stream);
+int b200q_buffer_d2h(int device, void *dst_host, const void *src_dev, size_t nbytes, void *stream);
+int b200q_stream_sync(int device, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H_ */

@@ -1,0 +1,526 @@
+/*
+ * CPU oracle for GGML block-quantized dense / embedding lookup.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file is the checker the CUDA path is compared
+ * against; nothing in the shipped library links or calls it.  It is a plain-C
+ * restatement of the reference's algorithm:
+ *
+ *   Q8_0 / Q4_0 dequantization    ml/ggml/dequant.go:56-115 (gomlx/gomlx)
+ *   dense = x @ dequant(W)^T      ml/ggml/dense.go:23-62
+ *   bias after matmul, act last   ml/ggml/dense.go:54-60
+ *   activations                   ml/layers/activation/activation.go:58-75,91-121
+ *   gather rows then dequantize   ml/ggml/gather.go:21-49
+ *
+ * Q4_K and Q6_K are executed by the reference inside the un-vendored module
+ * github.com/gomlx/compute v0.1.2 (call site core/graph/fused_ops.go:231);
+ * the reference repository holds no arithmetic and no test vector for them.
+ * They are restated here from the published GGML k-quant block format
+ * (144-byte Q4_K and 210-byte Q6_K super-blocks).  PARITY UNPINNED for those
+ * two formats: nothing in the reference's tests constrains them.
+ *
+ * Every f32 operation is individually rounded (compile with -ffp-contract=off).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+enum {
+    GGML_Q4_0 = 2,
+    GGML_Q8_0 = 8,
+    GGML_Q4_K = 12,
+    GGML_Q6_K = 14,
+};
+
+enum { ACT_NONE = 0, ACT_GELU = 1, ACT_RELU = 2, ACT_SILU = 3, ACT_HARDSWISH = 4, ACT_TANH = 5 };
+
+int oracle_bytes_per_block(int type) {
+    switch (type) {
+    case GGML_Q4_0: return 18;
+    case GGML_Q8_0: return 34;
+    case GGML_Q4_K: return 144;
+    case GGML_Q6_K: return 210;
+    default: return 0;
+    }
+}
+
+int oracle_values_per_block(int type) {
+    switch (type) {
+    case GGML_Q4_0:
+    case GGML_Q8_0: return 32;
+    case GGML_Q4_K:
+    case GGML_Q6_K: return 256;
+    default: return 0;
+    }
+}
+
+/* IEEE binary16 -> binary32, exact for every input (subnormals, inf, nan).
+ * The reference does Bitcast(u8 pair -> Float16, little endian) followed by
+ * ConvertDType(Float32): ml/ggml/dequant.go:63-65. */
+float oracle_fp16_to_f32(uint16_t h) {
+    uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    uint32_t exp = (h >> 10) & 0x1f;
+    uint32_t man = h & 0x3ffu;
+    uint32_t bits;
+    if (exp == 0) {
+        if (man == 0) {
+            bits = sign;
+        } else {
+            int e = -1;
+            do {
+                man <<= 1;
+                e++;
+            } while (!(man & 0x400u));
+            man &= 0x3ffu;
+            bits = sign | ((uint32_t)(127 - 15 - e) << 23) | (man << 13);
+        }
+    } else if (exp == 31) {
+        bits = sign | 0x7f800000u | (man << 13);
+    } else {
+        bits = sign | ((exp + 127 - 15) << 23) | (man << 13);
+    }
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+static inline float rd_fp16(const uint8_t *p) {
+    return oracle_fp16_to_f32((uint16_t)(p[0] | ((uint16_t)p[1] << 8)));
+}
+
+/* Q8_0: ml/ggml/dequant.go:58-78.  out[i] = f32(int8 q[i]) * f32(d). */
+static void dequant_row_q8_0(const uint8_t *row, int64_t k, float *out) {
+    int64_t nb = k / 32;
+    for (int64_t b = 0; b < nb; b++) {
+        const uint8_t *blk = row + b * 34;
+        float d = rd_fp16(blk);
+        for (int i = 0; i < 32; i++) out[b * 32 + i] = (float)(int8_t)blk[2 + i] * d;
+    }
+}
+
+/* Q4_0: ml/ggml/dequant.go:83-115.  Low nibbles are elements 0..15, high
+ * nibbles elements 16..31; out = (f32(nibble) - 8) * f32(d). */
+static void dequant_row_q4_0(const uint8_t *row, int64_t k, float *out) {
+    int64_t nb = k / 32;
+    for (int64_t b = 0; b < nb; b++) {
+        const uint8_t *blk = row + b * 18;
+        float d = rd_fp16(blk);
+        for (int j = 0; j < 16; j++) {
+            uint8_t q = blk[2 + j];
+            out[b * 32 + j] = ((float)(q & 0x0f) - 8.0f) * d;
+            out[b * 32 + 16 + j] = ((float)(q >> 4) - 8.0f) * d;
+        }
+    }
+}
+
+/* Q4_K six-bit scale / min for sub-block j of a super-block (GGML k-quant
+ * format: 12 bytes hold eight 6-bit scales and eight 6-bit mins). */
+void oracle_q4k_scale_min(const uint8_t *s, int j, uint8_t *sc, uint8_t *m) {
+    if (j < 4) {
+        *sc = s[j] & 63;
+        *m = s[j + 4] & 63;
+    } else {
+        *sc = (uint8_t)((s[j + 4] & 0x0f) | ((s[j - 4] >> 6) << 4));
+        *m = (uint8_t)((s[j + 4] >> 4) | ((s[j] >> 6) << 4));
+    }
+}
+
+/* Q4_K: block = fp16 d, fp16 dmin, scales[12], qs[128].  For each group of 64
+ * elements the 32 low nibbles come first, then the 32 high nibbles.
+ * w = (d*sc)*q - (dmin*m), three rounded f32 operations after the two
+ * rounded products. */
+static void dequant_row_q4_k(const uint8_t *row, int64_t k, float *out) {
+    int64_t nb = k / 256;
+    for (int64_t b = 0; b < nb; b++) {
+        const uint8_t *blk = row + b * 144;
+        float d = rd_fp16(blk);
+        float dmin = rd_fp16(blk + 2);
+        const uint8_t *scales = blk + 4;
+        const uint8_t *qs = blk + 16;
+        float *y = out + b * 256;
+        for (int g = 0; g < 4; g++) {
+            uint8_t sc, m;
+            oracle_q4k_scale_min(scales, 2 * g, &sc, &m);
+            float d1 = d * (float)sc;
+            float m1 = dmin * (float)m;
+            oracle_q4k_scale_min(scales, 2 * g + 1, &sc, &m);
+            float d2 = d * (float)sc;
+            float m2 = dmin * (float)m;
+            for (int l = 0; l < 32; l++) {
+                uint8_t q = qs[32 * g + l];
+                y[64 * g + l] = d1 * (float)(q & 0x0f) - m1;
+                y[64 * g + 32 + l] = d2 * (float)(q >> 4) - m2;
+            }
+        }
+    }
+}
+
+/* Q6_K: block = ql[128], qh[64], int8 scales[16], fp16 d.
+ * w = (d * scale) * (q - 32), two rounded f32 multiplies. */
+static void dequant_row_q6_k(const uint8_t *row, int64_t k, float *out) {
+    int64_t nb = k / 256;
+    for (int64_t b = 0; b < nb; b++) {
+        const uint8_t *blk = row + b * 210;
+        const uint8_t *ql = blk;
+        const uint8_t *qh = blk + 128;
+        const int8_t *sc = (const int8_t *)(blk + 192);
+        float d = rd_fp16(blk + 208);
+        float *y = out + b * 256;
+        for (int n = 0; n < 2; n++) {
+            for (int l = 0; l < 32; l++) {
+                int is = 8 * n + l / 16;
+                uint8_t h = qh[32 * n + l];
+                int q1 = (int)((ql[64 * n + l] & 0x0f) | (((h >> 0) & 3) << 4)) - 32;
+                int q2 = (int)((ql[64 * n + 32 + l] & 0x0f) | (((h >> 2) & 3) << 4)) - 32;
+                int q3 = (int)((ql[64 * n + l] >> 4) | (((h >> 4) & 3) << 4)) - 32;
+                int q4 = (int)((ql[64 * n + 32 + l] >> 4) | (((h >> 6) & 3) << 4)) - 32;
+                y[128 * n + l] = (d * (float)sc[is + 0]) * (float)q1;
+                y[128 * n + 32 + l] = (d * (float)sc[is + 2]) * (float)q2;
+                y[128 * n + 64 + l] = (d * (float)sc[is + 4]) * (float)q3;
+                y[128 * n + 96 + l] = (d * (float)sc[is + 6]) * (float)q4;
+            }
+        }
+    }
+}
+
+int oracle_dequant_row(int type, const uint8_t *row, int64_t k, float *out) {
+    switch (type) {
+    case GGML_Q8_0: dequant_row_q8_0(row, k, out); return 0;
+    case GGML_Q4_0: dequant_row_q4_0(row, k, out); return 0;
+    case GGML_Q4_K: dequant_row_q4_k(row, k, out); return 0;
+    case GGML_Q6_K: dequant_row_q6_k(row, k, out); return 0;
+    default: return -1;
+    }
+}
+
+/* ml/ggml/dequant.go:39-54: [N, nb*bpb] u8 -> [N, K] f32. */
+int oracle_dequantize(int type, const uint8_t *w, int64_t n, int64_t k, float *out, int threads) {
+    int vpb = oracle_values_per_block(type);
+    if (vpb == 0 || k % vpb) return -1;
+    int64_t bpr = k / vpb * oracle_bytes_per_block(type);
+#pragma omp parallel for schedule(static) num_threads(threads > 0 ? threads : 1)
+    for (int64_t r = 0; r < n; r++) oracle_dequant_row(type, w + r * bpr, k, out + r * k);
+    return 0;
+}
+
+static float apply_act(int act, float v) {
+    switch (act) {
+    case ACT_RELU: return v > 0.0f ? v : 0.0f;
+    case ACT_SILU: return v * (1.0f / (1.0f + expf(-v)));              /* x * sigmoid(x), activation.go:195-197 */
+    case ACT_GELU: return v * ((erff(v / 1.41421356237309504880f) + 1.0f) * 0.5f); /* exact erf form, activation.go:274-285 */
+    case ACT_HARDSWISH: {
+        float t = v * (1.0f / 6.0f) + 0.5f;                              /* x * clip(x*(1/6) + 1/2, 0, 1), activation.go:222-244 */
+        t = t < 0.0f ? 0.0f : (t > 1.0f ? 1.0f : t);
+        return v * t;
+    }
+    case ACT_TANH: return tanhf(v);
+    default: return v;
+    }
+}
+
+static double apply_act_f64(int act, double v) {
+    switch (act) {
+    case ACT_RELU: return v > 0.0 ? v : 0.0;
+    case ACT_SILU: return v / (1.0 + exp(-v));
+    case ACT_GELU: return v * ((erf(v / 1.41421356237309504880) + 1.0) * 0.5);
+    case ACT_HARDSWISH: {
+        double t = v * (1.0 / 6.0) + 0.5;
+        t = t < 0.0 ? 0.0 : (t > 1.0 ? 1.0 : t);
+        return v * t;
+    }
+    case ACT_TANH: return tanh(v);
+    default: return v;
+    }
+}
+
+/*
+ * "Decomposed" route, ml/ggml/dense.go:23-62: dequantize the whole W to f32
+ * [N,K], then y[m,n] = sum_k x[m,k] * W[n,k] with an f32 accumulator walking k
+ * in increasing order, then + bias, then activation.  `wbuf` is caller scratch
+ * of n*k floats (the materialised weight, as the reference materialises it).
+ */
+int oracle_dense_decomposed(int type, const uint8_t *w, int64_t n, int64_t k, const float *x, int64_t m,
+                            const float *bias, int act, float *y, float *wbuf, int threads) {
+    if (oracle_dequantize(type, w, n, k, wbuf, threads)) return -1;
+#pragma omp parallel for schedule(static) num_threads(threads > 0 ? threads : 1)
+    for (int64_t r = 0; r < n; r++) {
+        const float *wr = wbuf + r * k;
+        for (int64_t i = 0; i < m; i++) {
+            const float *xr = x + i * k;
+            float acc = 0.0f;
+            for (int64_t c = 0; c < k; c++) acc += xr[c] * wr[c];
+            if (bias) acc += bias[r];
+            y[i * n + r] = apply_act(act, acc);
+        }
+    }
+    return 0;
+}
+
+/*
+ * "Fused" route: same values, no materialised W — one row is dequantized into a
+ * small stack buffer and dotted at once (stand-in for the external fused
+ * executor reached at core/graph/fused_ops.go:231).  Eight independent f32
+ * partial sums per row so the compiler can vectorise; this is the route timed
+ * as the CPU baseline.
+ */
+int oracle_dense_fused(int type, const uint8_t *w, int64_t n, int64_t k, const float *x, int64_t m,
+                       const float *bias, int act, float *y, int threads) {
+    int vpb = oracle_values_per_block(type);
+    if (vpb == 0 || k % vpb) return -1;
+    int64_t bpr = k / vpb * oracle_bytes_per_block(type);
+    int bad = 0;
+#pragma omp parallel num_threads(threads > 0 ? threads : 1)
+    {
+        float *wr = (float *)malloc((size_t)k * sizeof(float));
+        if (!wr) {
+#pragma omp atomic write
+            bad = 1;
+        } else {
+#pragma omp for schedule(static)
+            for (int64_t r = 0; r < n; r++) {
+                oracle_dequant_row(type, w + r * bpr, k, wr);
+                for (int64_t i = 0; i < m; i++) {
+                    const float *xr = x + i * k;
+                    float p[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                    for (int64_t c = 0; c < k; c += 8)
+                        for (int u = 0; u < 8; u++) p[u] += xr[c + u] * wr[c + u];
+                    float acc = ((p[0] + p[1]) + (p[2] + p[3])) + ((p[4] + p[5]) + (p[6] + p[7]));
+                    if (bias) acc += bias[r];
+                    y[i * n + r] = apply_act(act, acc);
+                }
+            }
+        }
+        free(wr);
+    }
+    return bad ? -2 : 0;
+}
+
+/* Error yardstick: f64 accumulation of the exactly dequantized f32 weights. */
+int oracle_dense_f64(int type, const uint8_t *w, int64_t n, int64_t k, const float *x, int64_t m,
+                     const float *bias, int act, double *y, int threads) {
+    int vpb = oracle_values_per_block(type);
+    if (vpb == 0 || k % vpb) return -1;
+    int64_t bpr = k / vpb * oracle_bytes_per_block(type);
+#pragma omp parallel num_threads(threads > 0 ? threads : 1)
+    {
+        float *wr = (float *)malloc((size_t)k * sizeof(float));
+#pragma omp for schedule(static)
+        for (int64_t r = 0; r < n; r++) {
+            oracle_dequant_row(type, w + r * bpr, k, wr);
+            for (int64_t i = 0; i < m; i++) {
+                const float *xr = x + i * k;
+                double acc = 0.0;
+                for (int64_t c = 0; c < k; c++) acc += (double)xr[c] * (double)wr[c];
+                if (bias) acc += (double)bias[r];
+                y[i * n + r] = apply_act_f64(act, acc);
+            }
+        }
+        free(wr);
+    }
+    return 0;
+}
+
+/* ml/ggml/gather.go:21-49: pick rows by index, dequantize only those. */
+int oracle_embedding_lookup(int type, const uint8_t *table, int64_t vocab, int64_t k, const int32_t *idx,
+                            int64_t n_idx, float *out) {
+    int vpb = oracle_values_per_block(type);
+    if (vpb == 0 || k % vpb) return -1;
+    int64_t bpr = k / vpb * oracle_bytes_per_block(type);
+    for (int64_t i = 0; i < n_idx; i++) {
+        if (idx[i] < 0 || idx[i] >= vocab) return -2;
+        oracle_dequant_row(type, table + (int64_t)idx[i] * bpr, k, out + i * k);
+    }
+    return 0;
+}
+
+/* ------------------------------------------------------------------------- *
+ * Input manufacture.  These quantizers only produce valid packed bytes from
+ * seeded f32 weights; both the oracle and the CUDA path consume the bytes, so
+ * the rounding choices below are not a parity surface.
+ * ------------------------------------------------------------------------- */
+
+static uint16_t f32_to_fp16(float f) {
+    uint32_t x;
+    memcpy(&x, &f, 4);
+    uint32_t sign = (x >> 16) & 0x8000u;
+    int32_t e = (int32_t)((x >> 23) & 0xff) - 127 + 15;
+    uint32_t man = x & 0x7fffffu;
+    if (((x >> 23) & 0xff) == 0xff) return (uint16_t)(sign | 0x7c00u | (man ? 0x200u : 0));
+    if (e >= 31) return (uint16_t)(sign | 0x7c00u);
+    if (e <= 0) {
+        if (e < -10) return (uint16_t)sign;
+        man |= 0x800000u;
+        int shift = 14 - e;
+        uint32_t half = man >> shift;
+        uint32_t rem = man & ((1u << shift) - 1);
+        uint32_t mid = 1u << (shift - 1);
+        if (rem > mid || (rem == mid && (half & 1))) half++;
+        return (uint16_t)(sign | half);
+    }
+    uint32_t half = ((uint32_t)e << 10) | (man >> 13);
+    uint32_t rem = man & 0x1fffu;
+    if (rem > 0x1000u || (rem == 0x1000u && (half & 1))) half++;
+    return (uint16_t)(sign | half);
+}
+
+static inline void wr_fp16(uint8_t *p, float f) {
+    uint16_t h = f32_to_fp16(f);
+    p[0] = (uint8_t)(h & 0xff);
+    p[1] = (uint8_t)(h >> 8);
+}
+
+static inline int clampi(int v, int lo, int hi) { return v < lo ? lo : (v > hi ? hi : v); }
+
+static void quant_row_q8_0(const float *x, int64_t k, uint8_t *row) {
+    for (int64_t b = 0; b < k / 32; b++) {
+        float amax = 0;
+        for (int i = 0; i < 32; i++) amax = fmaxf(amax, fabsf(x[b * 32 + i]));
+        float d = amax / 127.0f;
+        uint8_t *blk = row + b * 34;
+        wr_fp16(blk, d);
+        float dq = rd_fp16(blk);
+        float id = dq != 0.0f ? 1.0f / dq : 0.0f;
+        for (int i = 0; i < 32; i++) blk[2 + i] = (uint8_t)(int8_t)clampi((int)lrintf(x[b * 32 + i] * id), -127, 127);
+    }
+}
+
+static void quant_row_q4_0(const float *x, int64_t k, uint8_t *row) {
+    for (int64_t b = 0; b < k / 32; b++) {
+        float amax = 0, vmax = 0;
+        for (int i = 0; i < 32; i++) {
+            float v = x[b * 32 + i];
+            if (fabsf(v) > amax) {
+                amax = fabsf(v);
+                vmax = v;
+            }
+        }
+        float d = vmax / -8.0f;
+        uint8_t *blk = row + b * 18;
+        wr_fp16(blk, d);
+        float dq = rd_fp16(blk);
+        float id = dq != 0.0f ? 1.0f / dq : 0.0f;
+        for (int j = 0; j < 16; j++) {
+            int lo = clampi((int)lrintf(x[b * 32 + j] * id) + 8, 0, 15);
+            int hi = clampi((int)lrintf(x[b * 32 + 16 + j] * id) + 8, 0, 15);
+            blk[2 + j] = (uint8_t)(lo | (hi << 4));
+        }
+    }
+}
+
+static void quant_row_q4_k(const float *x, int64_t k, uint8_t *row) {
+    for (int64_t b = 0; b < k / 256; b++) {
+        const float *xb = x + b * 256;
+        uint8_t *blk = row + b * 144;
+        float smin[8], sscale[8];
+        float max_scale = 0, max_min = 0;
+        for (int j = 0; j < 8; j++) {
+            float lo = xb[32 * j], hi = xb[32 * j];
+            for (int i = 1; i < 32; i++) {
+                lo = fminf(lo, xb[32 * j + i]);
+                hi = fmaxf(hi, xb[32 * j + i]);
+            }
+            if (lo > 0) lo = 0;
+            sscale[j] = (hi - lo) / 15.0f;
+            smin[j] = -lo;
+            max_scale = fmaxf(max_scale, sscale[j]);
+            max_min = fmaxf(max_min, smin[j]);
+        }
+        wr_fp16(blk, max_scale / 63.0f);
+        wr_fp16(blk + 2, max_min / 63.0f);
+        float d = rd_fp16(blk), dmin = rd_fp16(blk + 2);
+        float id = d != 0.0f ? 1.0f / d : 0.0f, idmin = dmin != 0.0f ? 1.0f / dmin : 0.0f;
+        uint8_t sc[8], mn[8];
+        for (int j = 0; j < 8; j++) {
+            sc[j] = (uint8_t)clampi((int)lrintf(sscale[j] * id), 0, 63);
+            mn[j] = (uint8_t)clampi((int)lrintf(smin[j] * idmin), 0, 63);
+        }
+        uint8_t *s = blk + 4;
+        memset(s, 0, 12);
+        for (int j = 0; j < 8; j++) {
+            if (j < 4) {
+                s[j] = sc[j];
+                s[j + 4] = mn[j];
+            } else {
+                s[j + 4] = (uint8_t)((sc[j] & 0x0f) | ((mn[j] & 0x0f) << 4));
+                s[j - 4] |= (uint8_t)((sc[j] >> 4) << 6);
+                s[j] |= (uint8_t)((mn[j] >> 4) << 6);
+            }
+        }
+        uint8_t q[256];
+        for (int j = 0; j < 8; j++) {
+            float ds = d * (float)sc[j], dm = dmin * (float)mn[j];
+            float ids = ds != 0.0f ? 1.0f / ds : 0.0f;
+            for (int i = 0; i < 32; i++) q[32 * j + i] = (uint8_t)clampi((int)lrintf((xb[32 * j + i] + dm) * ids), 0, 15);
+        }
+        uint8_t *qs = blk + 16;
+        for (int g = 0; g < 4; g++)
+            for (int l = 0; l < 32; l++) qs[32 * g + l] = (uint8_t)(q[64 * g + l] | (q[64 * g + 32 + l] << 4));
+    }
+}
+
+static void quant_row_q6_k(const float *x, int64_t k, uint8_t *row) {
+    for (int64_t b = 0; b < k / 256; b++) {
+        const float *xb = x + b * 256;
+        uint8_t *blk = row + b * 210;
+        float sub[16], max_abs = 0;
+        for (int s = 0; s < 16; s++) {
+            float amax = 0, vmax = 0;
+            for (int i = 0; i < 16; i++) {
+                float v = xb[16 * s + i];
+                if (fabsf(v) > amax) {
+                    amax = fabsf(v);
+                    vmax = v;
+                }
+            }
+            sub[s] = vmax / -32.0f;
+            max_abs = fmaxf(max_abs, fabsf(sub[s]));
+        }
+        wr_fp16(blk + 208, max_abs / 127.0f);
+        float d = rd_fp16(blk + 208);
+        float id = d != 0.0f ? 1.0f / d : 0.0f;
+        int8_t *sc = (int8_t *)(blk + 192);
+        uint8_t q[256];
+        for (int s = 0; s < 16; s++) {
+            sc[s] = (int8_t)clampi((int)lrintf(sub[s] * id), -128, 127);
+            float ds = d * (float)sc[s];
+            float ids = ds != 0.0f ? 1.0f / ds : 0.0f;
+            for (int i = 0; i < 16; i++) q[16 * s + i] = (uint8_t)clampi((int)lrintf(xb[16 * s + i] * ids) + 32, 0, 63);
+        }
+        uint8_t *ql = blk, *qh = blk + 128;
+        for (int n = 0; n < 2; n++)
+            for (int l = 0; l < 32; l++) {
+                uint8_t q1 = q[128 * n + l], q2 = q[128 * n + 32 + l], q3 = q[128 * n + 64 + l], q4 = q[128 * n + 96 + l];
+                ql[64 * n + l] = (uint8_t)((q1 & 0x0f) | ((q3 & 0x0f) << 4));
+                ql[64 * n + 32 + l] = (uint8_t)((q2 & 0x0f) | ((q4 & 0x0f) << 4));
+                qh[32 * n + l] = (uint8_t)((q1 >> 4) | ((q2 >> 4) << 2) | ((q3 >> 4) << 4) | ((q4 >> 4) << 6));
+            }
+    }
+}
+
+int oracle_quantize(int type, const float *x, int64_t n, int64_t k, uint8_t *out, int threads) {
+    int vpb = oracle_values_per_block(type);
+    if (vpb == 0 || k % vpb) return -1;
+    int64_t bpr = k / vpb * oracle_bytes_per_block(type);
+#pragma omp parallel for schedule(static) num_threads(threads > 0 ? threads : 1)
+    for (int64_t r = 0; r < n; r++) {
+        switch (type) {
+        case GGML_Q8_0: quant_row_q8_0(x + r * k, k, out + r * bpr); break;
+        case GGML_Q4_0: quant_row_q4_0(x + r * k, k, out + r * bpr); break;
+        case GGML_Q4_K: quant_row_q4_k(x + r * k, k, out + r * bpr); break;
+        case GGML_Q6_K: quant_row_q6_k(x + r * k, k, out + r * bpr); break;
+        }
+    }
+    return 0;
+}
+
+int oracle_max_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}

@@ -1,0 +1,216 @@
+"""CPU oracle for the GGML quantized dense path.  TEST INFRASTRUCTURE ONLY.
+
+Only the tests, the smoke check and the CPU-baseline leg of the benchmark may
+import this module; the product (``gomlx_b200``) never does.
+
+Two independent restatements of the reference algorithm live here:
+
+* ``ggml_oracle.c`` (loaded through ctypes): scalar C, one rounded f32 operation
+  per step, following gomlx/gomlx ``ml/ggml/dequant.go:56-115`` (Q8_0, Q4_0),
+  ``ml/ggml/dense.go:23-62`` (matmul, bias, activation order) and
+  ``ml/ggml/gather.go:21-49`` (row gather).
+* the ``np_dequant_*`` functions below: vectorised numpy written separately from
+  the C, used to cross-check it.
+
+Q4_K / Q6_K: the reference runs them in the un-vendored module
+github.com/gomlx/compute v0.1.2 and has no test vector for them, so both
+restatements follow the published GGML k-quant block format.  PARITY UNPINNED
+for those two formats.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
+ACT_NONE, ACT_GELU, ACT_RELU, ACT_SILU, ACT_HARDSWISH, ACT_TANH = range(6)
+BYTES_PER_BLOCK = {Q4_0: 18, Q8_0: 34, Q4_K: 144, Q6_K: 210}
+VALUES_PER_BLOCK = {Q4_0: 32, Q8_0: 32, Q4_K: 256, Q6_K: 256}
+TYPE_NAMES = {Q4_0: "Q4_0", Q8_0: "Q8_0", Q4_K: "Q4_K", Q6_K: "Q6_K"}
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "_build", "liboracle.so")
+_lib = None
+
+
+def build(force: bool = False) -> str:
+    """Compile ggml_oracle.c into oracle/_build/liboracle.so (gcc + OpenMP)."""
+    src = os.path.join(_HERE, "ggml_oracle.c")
+    if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-C", _HERE, "-B", "_build/liboracle.so"], stdout=subprocess.DEVNULL)
+    return _LIB_PATH
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            build()
+        L = ctypes.CDLL(_LIB_PATH)
+        i64, vp, ci = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int
+        L.oracle_dequantize.argtypes = [ci, vp, i64, i64, vp, ci]
+        L.oracle_dense_decomposed.argtypes = [ci, vp, i64, i64, vp, i64, vp, ci, vp, vp, ci]
+        L.oracle_dense_fused.argtypes = [ci, vp, i64, i64, vp, i64, vp, ci, vp, ci]
+        L.oracle_dense_f64.argtypes = [ci, vp, i64, i64, vp, i64, vp, ci, vp, ci]
+        L.oracle_embedding_lookup.argtypes = [ci, vp, i64, i64, vp, i64, vp]
+        L.oracle_quantize.argtypes = [ci, vp, i64, i64, vp, ci]
+        L.oracle_fp16_to_f32.argtypes = [ctypes.c_uint16]
+        L.oracle_fp16_to_f32.restype = ctypes.c_float
+        L.oracle_max_threads.restype = ci
+        _lib = L
+    return _lib
+
+
+def max_threads() -> int:
+    return int(lib().oracle_max_threads())
+
+
+def row_bytes(qtype: int, k: int) -> int:
+    vpb = VALUES_PER_BLOCK[qtype]
+    if k % vpb:
+        raise ValueError(f"K={k} is not a multiple of {vpb} for {TYPE_NAMES[qtype]}")
+    return k // vpb * BYTES_PER_BLOCK[qtype]
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
+
+
+def _check_w(qtype, w):
+    w = np.ascontiguousarray(w, dtype=np.uint8)
+    n, bpr = w.shape
+    bpb = BYTES_PER_BLOCK[qtype]
+    if bpr % bpb:
+        raise ValueError("row bytes not a multiple of the block size")
+    return w, n, bpr // bpb * VALUES_PER_BLOCK[qtype]
+
+
+def dequantize(qtype: int, w: np.ndarray, threads: int = 0) -> np.ndarray:
+    """[N, bytesPerRow] uint8 -> [N, K] float32 (ml/ggml/dequant.go:39-54)."""
+    w, n, k = _check_w(qtype, w)
+    out = np.empty((n, k), np.float32)
+    rc = lib().oracle_dequantize(qtype, _ptr(w), n, k, _ptr(out), threads or max_threads())
+    assert rc == 0, rc
+    return out
+
+
+def dense(qtype: int, w: np.ndarray, x: np.ndarray, bias=None, act: int = ACT_NONE, route: str = "decomposed",
+          threads: int = 0) -> np.ndarray:
+    """y = act(x @ dequant(w)^T + bias); route in {"decomposed", "fused", "f64"}."""
+    w, n, k = _check_w(qtype, w)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    lead = x.shape[:-1]
+    assert x.shape[-1] == k, (x.shape, k)
+    x2 = x.reshape(-1, k)
+    m = x2.shape[0]
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    t = threads or max_threads()
+    if route == "f64":
+        y = np.empty((m, n), np.float64)
+        rc = lib().oracle_dense_f64(qtype, _ptr(w), n, k, _ptr(x2), m, _ptr(b), act, _ptr(y), t)
+    elif route == "fused":
+        y = np.empty((m, n), np.float32)
+        rc = lib().oracle_dense_fused(qtype, _ptr(w), n, k, _ptr(x2), m, _ptr(b), act, _ptr(y), t)
+    else:
+        y = np.empty((m, n), np.float32)
+        wbuf = np.empty((n, k), np.float32)
+        rc = lib().oracle_dense_decomposed(qtype, _ptr(w), n, k, _ptr(x2), m, _ptr(b), act, _ptr(y), _ptr(wbuf), t)
+    assert rc == 0, rc
+    return y.reshape(*lead, n)
+
+
+def embedding_lookup(qtype: int, table: np.ndarray, indices: np.ndarray) -> np.ndarray:
+    """indices [..., 1] int32 -> [..., K] float32 (ml/ggml/gather.go:21-49)."""
+    table, vocab, k = _check_w(qtype, table)
+    idx = np.ascontiguousarray(indices, dtype=np.int32)
+    assert idx.shape[-1] == 1
+    flat = idx.reshape(-1)
+    out = np.empty((flat.size, k), np.float32)
+    rc = lib().oracle_embedding_lookup(qtype, _ptr(table), vocab, k, _ptr(flat), flat.size, _ptr(out))
+    if rc != 0:
+        raise IndexError("embedding index out of range")
+    return out.reshape(*idx.shape[:-1], k)
+
+
+def quantize(qtype: int, w_f32: np.ndarray, threads: int = 0) -> np.ndarray:
+    """Manufacture packed bytes from f32 weights [N, K] (inputs only, not a parity surface)."""
+    w = np.ascontiguousarray(w_f32, dtype=np.float32)
+    n, k = w.shape
+    out = np.empty((n, row_bytes(qtype, k)), np.uint8)
+    rc = lib().oracle_quantize(qtype, _ptr(w), n, k, _ptr(out), threads or max_threads())
+    assert rc == 0, rc
+    return out
+
+
+def make_weights(qtype: int, n: int, k: int, sigma: float = 0.02, seed: int = 0) -> np.ndarray:
+    """Seeded N(0, sigma) f32 weights quantized to `qtype` (numpy PCG64, default_rng(seed))."""
+    rng = np.random.default_rng(seed)
+    return quantize(qtype, rng.standard_normal((n, k), dtype=np.float32) * np.float32(sigma))
+
+
+# --------------------------------------------------------------------------- #
+# Independent numpy restatement (cross-check of the C file).
+# --------------------------------------------------------------------------- #
+
+def _f16(bytes2: np.ndarray) -> np.ndarray:
+    return np.ascontiguousarray(bytes2).view("<f2").astype(np.float32)
+
+
+def np_dequant_q8_0(w: np.ndarray) -> np.ndarray:
+    n = w.shape[0]
+    blk = w.reshape(n, -1, 34)
+    d = _f16(blk[:, :, 0:2])                                   # [n, nb, 1]
+    q = np.ascontiguousarray(blk[:, :, 2:]).view(np.int8).astype(np.float32)
+    return (q * d).reshape(n, -1)
+
+
+def np_dequant_q4_0(w: np.ndarray) -> np.ndarray:
+    n = w.shape[0]
+    blk = w.reshape(n, -1, 18)
+    d = _f16(blk[:, :, 0:2])
+    qs = blk[:, :, 2:]
+    vals = np.concatenate([qs & 0x0F, qs >> 4], axis=2).astype(np.float32)
+    return ((vals - np.float32(8.0)) * d).reshape(n, -1)
+
+
+def np_dequant_q4_k(w: np.ndarray) -> np.ndarray:
+    n = w.shape[0]
+    blk = w.reshape(n, -1, 144)
+    d = _f16(blk[:, :, 0:2])[..., 0]
+    dmin = _f16(blk[:, :, 2:4])[..., 0]
+    s = blk[:, :, 4:16].astype(np.uint8)
+    sc = np.empty(s.shape[:2] + (8,), np.uint8)
+    mn = np.empty_like(sc)
+    sc[..., :4] = s[..., 0:4] & 63
+    mn[..., :4] = s[..., 4:8] & 63
+    sc[..., 4:] = (s[..., 8:12] & 0x0F) | ((s[..., 0:4] >> 6) << 4)
+    mn[..., 4:] = (s[..., 8:12] >> 4) | ((s[..., 4:8] >> 6) << 4)
+    qs = blk[:, :, 16:].reshape(n, -1, 4, 32)
+    q = np.stack([qs & 0x0F, qs >> 4], axis=3).reshape(n, -1, 8, 32).astype(np.float32)
+    ds = (d[..., None] * sc.astype(np.float32))[..., None]
+    dm = (dmin[..., None] * mn.astype(np.float32))[..., None]
+    return (ds * q - dm).astype(np.float32).reshape(n, -1)
+
+
+def np_dequant_q6_k(w: np.ndarray) -> np.ndarray:
+    n = w.shape[0]
+    blk = w.reshape(n, -1, 210)
+    nb = blk.shape[1]
+    ql = blk[:, :, 0:128].reshape(n, nb, 2, 2, 32)      # [half n][first/second 32 bytes][l]
+    qh = blk[:, :, 128:192].reshape(n, nb, 2, 32)
+    sc = np.ascontiguousarray(blk[:, :, 192:208]).view(np.int8).astype(np.float32).reshape(n, nb, 2, 4, 2)
+    d = _f16(blk[:, :, 208:210])[..., 0]
+    q = np.empty((n, nb, 2, 4, 32), np.int32)
+    q[:, :, :, 0] = (ql[:, :, :, 0] & 0x0F) | (((qh >> 0) & 3) << 4)
+    q[:, :, :, 1] = (ql[:, :, :, 1] & 0x0F) | (((qh >> 2) & 3) << 4)
+    q[:, :, :, 2] = (ql[:, :, :, 0] >> 4) | (((qh >> 4) & 3) << 4)
+    q[:, :, :, 3] = (ql[:, :, :, 1] >> 4) | (((qh >> 6) & 3) << 4)
+    q = (q - 32).astype(np.float32).reshape(n, nb, 2, 4, 2, 16)
+    ds = (d[:, :, None, None, None] * sc)[..., None]
+    return (ds * q).astype(np.float32).reshape(n, -1)
+
+
+NP_DEQUANT = {Q8_0: np_dequant_q8_0, Q4_0: np_dequant_q4_0, Q4_K: np_dequant_q4_k, Q6_K: np_dequant_q6_k}

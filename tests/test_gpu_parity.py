@@ -1,0 +1,260 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle.  Needs a B200."""
+import ctypes
+import json
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+import gomlx_b200 as g  # noqa: E402
+from gomlx_b200 import _native as nat  # noqa: E402
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+TYPES = {"Q8_0": g.GGMLQuantType.Q8_0, "Q4_0": g.GGMLQuantType.Q4_0, "Q4_K": g.GGMLQuantType.Q4_K,
+         "Q6_K": g.GGMLQuantType.Q6_K}
+ACT = {"none": g.Activation.NONE, "silu": g.Activation.SILU, "gelu": g.Activation.GELU, "relu": g.Activation.RELU,
+       "hard_swish": g.Activation.HARD_SWISH, "tanh": g.Activation.TANH}
+# north star: max relative error <= 2e-3 with f32 accumulation; "relative" = max |err| / max |reference|.
+TOL_GEMV = 2e-3
+TOL_GEMM = 1e-2
+
+
+def quant(t):
+    return g.Quantization(g.QuantizationScheme.GGML, t)
+
+
+def rel_err(y, ref):
+    ref = np.asarray(ref, np.float64)
+    return float(np.abs(np.asarray(y, np.float64) - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+def same_bits(a, b):
+    a, b = np.asarray(a, np.float32), np.asarray(b, np.float32)
+    return bool(((a.view(np.uint32) == b.view(np.uint32)) | (np.isnan(a) & np.isnan(b))).all())
+
+
+def kats():
+    with open(os.path.join(GOLDEN, "reference_kats.json")) as f:
+        return json.load(f)
+
+
+# ----------------------------------------------------------------------------- reference KATs
+@pytest.mark.parametrize("case", kats()["dense"], ids=lambda c: c["name"])
+@pytest.mark.parametrize("where", ["device", "host"])
+def test_reference_dense_kats(case, where):
+    t = g.GGMLQuantType(case["type"])
+    w = np.array(case["w"], np.uint8)
+    x = np.array(case["x"], np.float32)
+    bias = None if case["bias"] is None else np.array(case["bias"], np.float32)
+    want = np.array(case["want"], np.float32)
+    for _ in range(2):  # the reference harness runs every graph twice (graphtest.go:54-107)
+        if where == "device":
+            y = g.quantized_dense(torch.from_numpy(x).cuda(), w, quant(t),
+                                  None if bias is None else torch.from_numpy(bias).cuda(), ACT[case["act"]]).cpu().numpy()
+        else:
+            y = g.quantized_dense(x, w, quant(t), bias, ACT[case["act"]])
+        np.testing.assert_allclose(y, want, rtol=0, atol=case["delta"])
+
+
+@pytest.mark.parametrize("case", kats()["gather"], ids=lambda c: c["name"])
+@pytest.mark.parametrize("where", ["device", "host"])
+def test_reference_gather_kats(case, where):
+    t = g.GGMLQuantType(case["type"])
+    table = np.array(case["table"], np.uint8)
+    idx = np.array(case["indices"], np.int32)
+    out = g.quantized_gather(table, torch.from_numpy(idx).cuda() if where == "device" else idx, quant(t))
+    out = out.cpu().numpy() if where == "device" else out
+    np.testing.assert_allclose(out, np.array(case["want"], np.float32), rtol=0, atol=case["delta"])
+
+
+# ----------------------------------------------------------------------------- dequantize: bit-exact
+@pytest.mark.parametrize("name", list(TYPES))
+@pytest.mark.parametrize("n,kblocks", [(1, 1), (17, 2), (40, 5), (300, 16)])
+def test_dequantize_bit_exact(oracle, name, n, kblocks):
+    t = TYPES[name]
+    k = kblocks * t.values_per_block()
+    w = oracle.make_weights(int(t), n, k, seed=n + kblocks)
+    assert same_bits(g.dequantize(w, t), oracle.dequantize(int(t), w))
+    raw = np.random.default_rng(n).integers(0, 256, size=w.shape, dtype=np.uint8)  # every header bit pattern
+    assert same_bits(g.dequantize(raw, t), oracle.dequantize(int(t), raw))
+
+
+@pytest.mark.parametrize("name", list(TYPES))
+def test_committed_fixtures(name):
+    fx = np.load(os.path.join(GOLDEN, "kquant_fixtures.npz"))
+    t = TYPES[name]
+    assert same_bits(g.dequantize(fx[f"{name}_w"], t), fx[f"{name}_deq"])
+    rows = slice(0, fx[f"{name}_w"].shape[0] - 1)  # the last row is raw random bytes (huge scales)
+    y = g.quantized_dense(fx[f"{name}_x"], np.ascontiguousarray(fx[f"{name}_w"][rows]), quant(t))
+    assert rel_err(y, fx[f"{name}_y"][:, rows]) <= TOL_GEMV
+
+
+# ----------------------------------------------------------------------------- decode GEMV parity
+@pytest.mark.parametrize("name", list(TYPES))
+@pytest.mark.parametrize("m", [1, 2, 5, 8, 9, 16])
+@pytest.mark.parametrize("n,ktiles", [(16, 1), (100, 2.5), (1030, 4)])
+def test_gemv_parity(oracle, name, m, n, ktiles):
+    t = TYPES[name]
+    tk = 512 if name in ("Q8_0", "Q4_0") else 1024
+    k = int(ktiles * tk) // t.values_per_block() * t.values_per_block()
+    w = oracle.make_weights(int(t), n, k, seed=7)
+    rng = np.random.default_rng(m * 1000 + n)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    ref = oracle.dense(int(t), w, x, route="f64")
+    xd = torch.from_numpy(x).cuda()
+    y = g.quantized_dense(xd, w, quant(t))
+    assert g.last_kernel() == nat.KERNEL_GEMV_MMA
+    assert y.shape == (m, n) and y.dtype == torch.float32
+    assert rel_err(y.cpu().numpy(), ref) <= TOL_GEMV
+    assert torch.equal(y, g.quantized_dense(xd, w, quant(t)))  # deterministic
+
+
+@pytest.mark.parametrize("name", list(TYPES))
+@pytest.mark.parametrize("act", list(ACT))
+def test_gemv_bias_activation_bf16(oracle, name, act):
+    t = TYPES[name]
+    n, k, m = 200, 2048, 4
+    w = oracle.make_weights(int(t), n, k, sigma=0.05, seed=3)
+    rng = np.random.default_rng(9)
+    xb = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    bias = rng.standard_normal(n).astype(np.float32)
+    ref = oracle.dense(int(t), w, xb.float().cpu().numpy(), bias, int(ACT[act].to_backend()), route="f64")
+    y = g.quantized_dense(xb, w, quant(t), torch.from_numpy(bias).cuda(), ACT[act])
+    assert rel_err(y.cpu().numpy(), ref) <= TOL_GEMV
+
+
+def test_unsupported_activation_is_dropped(oracle):
+    t = g.GGMLQuantType.Q8_0
+    w = oracle.make_weights(8, 32, 512, seed=1)
+    x = torch.randn(2, 512, device="cuda")
+    assert torch.equal(g.quantized_dense(x, w, quant(t), None, g.Activation.LEAKY_RELU), g.quantized_dense(x, w, quant(t)))
+
+
+def test_batch_dims_are_restored(oracle):
+    t = g.GGMLQuantType.Q4_K
+    w = oracle.make_weights(12, 48, 1024, seed=1)
+    x = torch.randn(2, 3, 1024, device="cuda")
+    y = g.quantized_dense(x, w, quant(t))
+    assert y.shape == (2, 3, 48)
+    assert torch.equal(y.reshape(6, 48), g.quantized_dense(x.reshape(6, 1024), w, quant(t)))
+
+
+# ----------------------------------------------------------------------------- BASELINE shapes
+@pytest.mark.parametrize("name,n,k,sigma,ms", [
+    ("Q8_0", 4096, 4096, 0.02, [1]),                 # configs[0]
+    ("Q4_0", 14336, 4096, 0.02, [1, 4, 8, 16]),      # configs[1]
+    ("Q4_K", 14336, 4096, 0.02, [1, 8]),             # configs[3] gate/up
+    ("Q6_K", 4096, 14336, 0.02, [1, 8]),             # configs[3] down
+])
+def test_baseline_shapes_full_oracle(oracle, name, n, k, sigma, ms):
+    t = TYPES[name]
+    w = oracle.make_weights(int(t), n, k, sigma=sigma, seed=0)
+    wr = g.upload(w, t)
+    try:
+        for m in ms:
+            x = np.random.default_rng(m).standard_normal((m, k)).astype(np.float32)
+            ref = oracle.dense(int(t), w, x, route="fused")  # the f32 CPU route the reference would take
+            y = g.quantized_dense(torch.from_numpy(x).cuda(), wr, quant(t)).cpu().numpy()
+            assert rel_err(y, ref) <= TOL_GEMV, (name, m)
+    finally:
+        wr.free()
+
+
+@pytest.mark.parametrize("n,k", [(28672, 8192), (8192, 28672)])  # configs[4], 70B-shaped MLP, Q8_0
+def test_70b_shapes_sampled_rows_and_sharding(oracle, n, k):
+    t = g.GGMLQuantType.Q8_0
+    rng = np.random.default_rng(0)
+    # one seeded 1024-row band is tiled to the full height: values repeat, bytes and shapes are full size
+    band = oracle.make_weights(8, 1024, k, sigma=0.015, seed=0)
+    w = np.tile(band, (n // 1024, 1))
+    wr = g.upload(w, t)
+    x = rng.standard_normal((16, k)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    y = g.quantized_dense(xd, wr, quant(t))
+    rows = np.sort(rng.choice(n, 256, replace=False))
+    ref = oracle.dense(8, np.ascontiguousarray(w[rows]), x, route="f64")
+    assert rel_err(y[:, rows].cpu().numpy(), ref) <= TOL_GEMV
+    # linearity in x (up to the fp16 staging of activations)
+    y2 = g.quantized_dense(xd * 2.0, wr, quant(t))
+    assert torch.equal(y2, y * 2.0)  # scaling by a power of two is exact in every rounding step
+    # a row shard computes exactly the corresponding slice of the full result
+    for rank in (0, 5):
+        ws = g.upload(w, t, shard=(rank, 8))
+        ys = g.quantized_dense(xd, ws, quant(t))
+        assert torch.equal(ys, y[:, ws.row_begin:ws.row_begin + ws.n])
+        ws.free()
+    wr.free()
+
+
+# ----------------------------------------------------------------------------- gather
+@pytest.mark.parametrize("name", list(TYPES))
+def test_gather_random(oracle, name):
+    t = TYPES[name]
+    table = oracle.make_weights(int(t), 500, 1024, seed=2)
+    idx = np.random.default_rng(4).integers(0, 500, size=(3, 7, 1)).astype(np.int32)
+    out = g.quantized_gather(table, torch.from_numpy(idx).cuda(), quant(t))
+    assert out.shape == (3, 7, 1024)
+    assert same_bits(out.cpu().numpy(), oracle.embedding_lookup(int(t), table, idx))
+    assert same_bits(g.quantized_gather(table, idx, quant(t)), oracle.embedding_lookup(int(t), table, idx))
+    assert g.quantized_gather(table, torch.zeros((0, 1), dtype=torch.int32, device="cuda"), quant(t)).shape == (0, 1024)
+
+
+def test_gather_bad_index_is_an_error_not_a_fault(oracle):
+    t = g.GGMLQuantType.Q8_0
+    table = oracle.make_weights(8, 10, 64, seed=2)
+    wr = g.upload(table, t)
+    with pytest.raises(g.B200QError) as e:
+        g.quantized_gather(wr, torch.tensor([[3], [10]], dtype=torch.int32, device="cuda"), quant(t))
+    assert e.value.code == nat.EINVAL
+    with pytest.raises(g.B200QError):
+        g.quantized_gather(wr, np.array([[-1]], np.int32), quant(t))
+    ok = g.quantized_gather(wr, np.array([[9]], np.int32), quant(t))  # context still healthy
+    assert same_bits(ok, oracle.embedding_lookup(8, table, np.array([[9]], np.int32)))
+    wr.free()
+
+
+# ----------------------------------------------------------------------------- residency and errors
+def test_weight_residency(oracle):
+    L = nat.lib()
+    t = g.GGMLQuantType.Q4_0
+    w = oracle.make_weights(2, 64, 512, seed=1)
+    base = L.b200q_weight_live_count()
+    q = quant(t)
+    x = torch.randn(1, 512, device="cuda")
+    y1 = g.quantized_dense(x, w, q)
+    assert L.b200q_weight_live_count() == base + 1
+    y2 = g.quantized_dense(x, w, q)  # same host buffer: no second upload
+    assert L.b200q_weight_live_count() == base + 1 and torch.equal(y1, y2)
+    r = g.resident(w, q)
+    assert (r.n, r.k, r.device) == (64, 512, 0) and r.device_bytes == 4 * 1 * 4608
+    del r, w
+    import gc
+    gc.collect()
+    assert L.b200q_weight_live_count() == base  # released with the host buffer
+    wr = g.upload(oracle.make_weights(2, 16, 512, seed=1), t)
+    h = wr.handle
+    wr.free()
+    assert L.b200q_weight_free(h) == nat.EHANDLE
+
+
+def test_argument_errors(oracle):
+    t = g.GGMLQuantType.Q8_0
+    w = oracle.make_weights(8, 32, 512, seed=1)
+    with pytest.raises(ValueError):
+        g.quantized_dense(torch.randn(1, 256, device="cuda"), w, quant(t))  # wrong K
+    with pytest.raises(ValueError):
+        g.quantized_dense(torch.randn(1, 512, device="cuda", dtype=torch.float16), w, quant(t))
+    with pytest.raises(ValueError):
+        g.upload(w[:, :-1], t)
+    assert g.quantized_dense(torch.zeros(0, 512, device="cuda"), w, quant(t)).shape == (0, 32)
+    wr = g.resident(w, quant(t))
+    x = torch.randn(1, 520, device="cuda")[:, 4:516].contiguous()
+    bad = ctypes.c_void_p(x.data_ptr() + 4)
+    y = torch.empty(1, 32, device="cuda")
+    rc = nat.lib().b200q_dense(wr.handle, bad, nat.F32, 1, None, 0, ctypes.c_void_p(y.data_ptr()), 0, None)
+    assert rc == nat.EINVAL and b"aligned" in nat.lib().b200q_last_error()
+    rc = nat.lib().b200q_dense(wr.handle, ctypes.c_void_p(x.data_ptr()), 7, 1, None, 0, ctypes.c_void_p(y.data_ptr()), 0, None)
+    assert rc == nat.EINVAL

@@ -1,0 +1,72 @@
+"""Host-side mirror of the reference API: enums, validation and error mapping (no GPU needed)."""
+import numpy as np
+import pytest
+
+import gomlx_b200 as g
+from gomlx_b200 import _native as nat
+
+
+def test_ggml_type_metadata():
+    T = g.GGMLQuantType
+    assert (T.Q8_0.bytes_per_block(), T.Q8_0.values_per_block(), str(T.Q8_0)) == (34, 32, "Q8_0")
+    assert (T.Q4_0.bytes_per_block(), T.Q4_K.bytes_per_block(), T.Q6_K.bytes_per_block()) == (18, 144, 210)
+    assert g.can_decompose(T.Q4_0) and g.can_decompose(T.Q8_0) and g.can_decompose(T.IQ4NL)
+    assert not g.can_decompose(T.Q4_K) and not g.can_decompose(T.Q6_K)
+    assert g.row_bytes(T.Q4_K, 4096) == 2304 and g.logical_k(T.Q6_K, 210 * 16) == 4096
+    with pytest.raises(ValueError):
+        g.row_bytes(T.Q4_K, 4096 + 32)
+
+
+def test_activation_to_backend_matches_reference_table():
+    A, B = g.Activation, g.ActivationType
+    assert A.NONE.to_backend() == B.NONE
+    assert A.GELU.to_backend() == B.GELU and A.GELU_APPROX.to_backend() == B.GELU
+    assert A.SILU.to_backend() == B.SILU and A.SWISH.to_backend() == B.SILU
+    assert A.RELU.to_backend() == B.RELU and A.HARD_SWISH.to_backend() == B.HARD_SWISH and A.TANH.to_backend() == B.TANH
+    # everything else is dropped silently on the fused route (activation.go:72-74)
+    for a in (A.LEAKY_RELU, A.SIGMOID, A.HARD_SIGMOID, A.SELU, A.SWIGLU):
+        assert a.to_backend() == B.NONE
+
+
+def test_quantized_dense_validation():
+    q = g.Quantization(g.QuantizationScheme.GGML, g.GGMLQuantType.Q8_0)
+    x = np.zeros((1, 32), np.float32)
+    w = np.zeros((2, 34), np.uint8)
+    with pytest.raises(ValueError, match="only take one optional activation"):
+        g.quantized_dense(x, w, q, None, g.Activation.RELU, g.Activation.TANH)
+    with pytest.raises(ValueError, match="must not be None"):
+        g.backend_fused_quantized_dense(x, w, None, None)
+    lin = g.Quantization(g.QuantizationScheme.LINEAR)
+    with pytest.raises(ValueError, match="scale must not be None"):
+        g.backend_fused_quantized_dense(x, w, None, lin)
+    lin.scale = np.ones((32, 1), np.float32)
+    with pytest.raises(g.NotImplementedByBackend):  # caller falls back to the decomposed graph
+        g.backend_fused_quantized_dense(x, w, None, lin)
+    with pytest.raises(ValueError, match="only QuantGGML"):
+        g.quantized_gather(w, np.zeros((1, 1), np.int32), lin)
+
+
+def test_no_cpu_fallback_without_gpu():
+    """Without a CUDA device a compute call must fail loudly, never compute on the host."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("this check is for GPU-less machines")
+    q = g.Quantization(g.QuantizationScheme.GGML, g.GGMLQuantType.Q8_0)
+    w = np.zeros((2, 34), np.uint8)
+    with pytest.raises(g.B200QError) as e:
+        g.quantized_dense(np.zeros((1, 32), np.float32), w, q)
+    assert e.value.code in (nat.ECUDA, nat.ENOMEM)
+    iq = g.Quantization(g.QuantizationScheme.GGML, g.GGMLQuantType.IQ4NL)
+    with pytest.raises(g.NotImplementedByBackend):
+        g.quantized_dense(np.zeros((1, 32), np.float32), np.zeros((2, 18), np.uint8), iq)
+
+
+def test_product_does_not_import_oracle():
+    import os
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for dirpath, _, files in os.walk(os.path.join(root, "gomlx_b200")):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h", ".hpp", ".cpp")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert not re.search(r"^\s*(from|import)\s+oracle|#include\s+\".*oracle", text, re.M), f

@@ -1,0 +1,106 @@
+"""The CPU oracle against the reference's own known-answer vectors and against itself."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+ACTS = {"none": 0, "gelu": 1, "relu": 2, "silu": 3, "hard_swish": 4, "tanh": 5}
+
+
+def kats():
+    with open(os.path.join(GOLDEN, "reference_kats.json")) as f:
+        return json.load(f)
+
+
+@pytest.mark.parametrize("case", kats()["dense"], ids=lambda c: c["name"])
+@pytest.mark.parametrize("route", ["decomposed", "fused", "f64"])
+def test_reference_dense_kats(oracle, case, route):
+    w = np.array(case["w"], np.uint8)
+    x = np.array(case["x"], np.float32)
+    bias = None if case["bias"] is None else np.array(case["bias"], np.float32)
+    y = oracle.dense(case["type"], w, x, bias, ACTS[case["act"]], route=route, threads=1)
+    np.testing.assert_allclose(y, np.array(case["want"]), rtol=0, atol=case["delta"])
+
+
+@pytest.mark.parametrize("case", kats()["gather"], ids=lambda c: c["name"])
+def test_reference_gather_kats(oracle, case):
+    out = oracle.embedding_lookup(case["type"], np.array(case["table"], np.uint8), np.array(case["indices"], np.int32))
+    np.testing.assert_allclose(out, np.array(case["want"]), rtol=0, atol=case["delta"])
+
+
+def test_fp16_conversion_exhaustive(oracle):
+    bits = np.arange(65536, dtype=np.uint16)
+    want = bits.view(np.float16).astype(np.float32).view(np.uint32)
+    got = np.array([oracle.lib().oracle_fp16_to_f32(int(b)) for b in bits], np.float32).view(np.uint32)
+    nan = np.isnan(bits.view(np.float16))
+    assert np.array_equal(got[~nan], want[~nan])
+    assert np.all(np.isnan(got.view(np.float32)[nan]))
+
+
+@pytest.mark.parametrize("name", ["Q8_0", "Q4_0", "Q4_K", "Q6_K"])
+def test_c_and_numpy_restatements_agree(oracle, name):
+    t = {v: k for k, v in oracle.TYPE_NAMES.items()}[name]
+    rng = np.random.default_rng(11)
+    n, k = 7, 1024
+    raw = rng.integers(0, 256, size=(n, oracle.row_bytes(t, k)), dtype=np.uint8)
+    a, b = oracle.dequantize(t, raw, threads=1), oracle.NP_DEQUANT[t](raw)
+    same = (a.view(np.uint32) == b.view(np.uint32)) | (np.isnan(a) & np.isnan(b))
+    assert same.all()
+    w = oracle.make_weights(t, n, k, seed=5)
+    assert np.array_equal(oracle.dequantize(t, w).view(np.uint32), oracle.NP_DEQUANT[t](w).view(np.uint32))
+
+
+@pytest.mark.parametrize("name", ["Q8_0", "Q4_0", "Q4_K", "Q6_K"])
+def test_committed_fixtures(oracle, name):
+    fx = np.load(os.path.join(GOLDEN, "kquant_fixtures.npz"))
+    t = {v: k for k, v in oracle.TYPE_NAMES.items()}[name]
+    deq = oracle.dequantize(t, fx[f"{name}_w"], threads=1)
+    assert np.array_equal(deq.view(np.uint32), fx[f"{name}_deq"].view(np.uint32))
+    y = oracle.dense(t, fx[f"{name}_w"], fx[f"{name}_x"], route="decomposed", threads=1)
+    assert np.array_equal(y.view(np.uint32), fx[f"{name}_y"].view(np.uint32))
+
+
+@pytest.mark.parametrize("name", ["Q8_0", "Q4_0", "Q4_K", "Q6_K"])
+def test_routes_agree_and_quantizer_round_trip(oracle, name):
+    t = {v: k for k, v in oracle.TYPE_NAMES.items()}[name]
+    rng = np.random.default_rng(3)
+    n, k, m = 33, 1024, 3
+    wf = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+    w = oracle.quantize(t, wf)
+    deq = oracle.dequantize(t, w)
+    step = {"Q8_0": 1 / 127, "Q4_0": 1 / 8, "Q4_K": 1 / 15, "Q6_K": 1 / 32}[name]
+    assert np.abs(deq - wf).max() <= np.abs(wf).max() * step * 1.05
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    ref = oracle.dense(t, w, x, bias, 3, route="f64")
+    for route in ("decomposed", "fused"):
+        y = oracle.dense(t, w, x, bias, 3, route=route)
+        assert np.abs(y - ref).max() / np.abs(ref).max() < 1e-5
+    # dense == x @ dequant^T, batch dims are flattened and restored (dense.go:44-52)
+    y3 = oracle.dense(t, w, x.reshape(1, m, k), route="f64")
+    assert y3.shape == (1, m, n)
+    np.testing.assert_allclose(y3[0], x.astype(np.float64) @ deq.astype(np.float64).T, rtol=1e-12, atol=1e-12)
+
+
+def test_activations(oracle):
+    w = np.array(kats()["dense"][0]["w"], np.uint8)  # dequant rows: [2,0,...], [0,3,...]
+    for v in (-3.0, -0.5, 0.0, 0.7, 4.0):
+        x = np.zeros((1, 32), np.float32)
+        x[0, 0] = v / 2.0
+        for name, f in {
+            "relu": lambda z: max(z, 0.0),
+            "silu": lambda z: z / (1 + np.exp(-z)),
+            "tanh": np.tanh,
+            "hard_swish": lambda z: z * min(max(z / 6 + 0.5, 0), 1),
+            "gelu": lambda z: 0.5 * z * (1 + float(__import__("math").erf(z / np.sqrt(2)))),
+        }.items():
+            y = oracle.dense(8, w, x, None, ACTS[name], threads=1)
+            assert abs(y[0, 0] - f(v)) < 1e-5, (name, v)
+
+
+def test_gather_rejects_bad_index(oracle):
+    t = np.array(kats()["gather"][0]["table"], np.uint8)
+    with pytest.raises(IndexError):
+        oracle.embedding_lookup(8, t, np.array([[3]], np.int32))
