@@ -30,6 +30,7 @@ SYMBOLS = {
     "b200q_weight_upload": (_i, [_i, _i, _i64, _i64, _vp, _i64, _i, _pu64]),
     "b200q_weight_free": (_i, [_u64]),
     "b200q_weight_info": (_i, [_u64, _pi, _pi64, _pi64, _pi, _pi64]),
+    "b200q_weight_check": (_i, [_u64, _vp]),
     "b200q_weight_live_count": (_i, []),
     "b200q_dequantize": (_i, [_u64, _vp, _vp]),
     "b200q_dense": (_i, [_u64, _vp, _i, _i64, _vp, _i, _vp, _i64, _vp]),

@@ -176,6 +176,20 @@ int b200q_weight_info(b200q_weight_t h, int *ggml_type, int64_t *n_rows, int64_t
     return B200Q_OK;
 }
 
+int b200q_weight_check(b200q_weight_t h, void *stream) {
+    auto w = find(h);
+    if (!w) return fail(B200Q_EHANDLE, "weight_check: unknown handle");
+    B200Q_CUDA(cudaSetDevice(w->device));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int st = 0;
+    B200Q_CUDA(cudaMemcpyAsync(&st, w->status, sizeof(int), cudaMemcpyDeviceToHost, s));
+    B200Q_CUDA(cudaStreamSynchronize(s));
+    if (st == 0) return B200Q_OK;
+    B200Q_CUDA(cudaMemsetAsync(w->status, 0, sizeof(int), s));
+    if (st == 2) return fail(B200Q_ETIMEOUT, "a kernel gave up waiting for a tile copy");
+    return fail(B200Q_EINVAL, "embedding_lookup: index out of range");
+}
+
 int b200q_weight_live_count(void) {
     std::lock_guard<std::mutex> lk(g_mu);
     return (int)g_weights.size();
@@ -248,6 +262,7 @@ int b200q_dense_host(b200q_weight_t h, const void *x_host, int x_dtype, int64_t 
         if (rc != 0) break;
         if ((e = cudaMemcpyAsync(y_host, dev + yo, yb, cudaMemcpyDeviceToHost, 0)) != cudaSuccess) { rc = cuda_fail(e, "D2H y"); break; }
         if ((e = cudaStreamSynchronize(0)) != cudaSuccess) { rc = cuda_fail(e, "dense_host sync"); break; }
+        rc = b200q_weight_check(h, nullptr);
     } while (0);
     cudaFree(dev);
     return rc;

@@ -101,6 +101,11 @@ int b200q_weight_upload(int device, int ggml_type, int64_t n_rows, int64_t k, co
 int b200q_weight_free(b200q_weight_t w);
 int b200q_weight_info(b200q_weight_t w, int *ggml_type, int64_t *n_rows, int64_t *k, int *device,
                       int64_t *device_bytes);
+/* Synchronises `stream` and reports what kernels that used this weight recorded on the device
+ * since the last check: B200Q_ETIMEOUT if a bounded device-side wait gave up, B200Q_EINVAL
+ * if an embedding index was out of range, else B200Q_OK.  Clears the record.  (The Go
+ * error return of Executable.Execute, core/graph/graph.go:669-675.) */
+int b200q_weight_check(b200q_weight_t w, void *stream);
 /* Number of resident weights (leak checks). */
 int b200q_weight_live_count(void);
 
