@@ -70,3 +70,18 @@ def test_product_does_not_import_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h", ".hpp", ".cpp")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert not re.search(r"^\s*(from|import)\s+oracle|#include\s+\".*oracle", text, re.M), f
+
+
+@pytest.mark.parametrize("name", ["Q8_0", "Q4_0", "Q4_K", "Q6_K"])
+def test_numpy_quantizers_make_valid_blocks(oracle, name):
+    from gomlx_b200 import quantize as qz
+    t = g.GGMLQuantType[name]
+    rng = np.random.default_rng(0)
+    w = rng.standard_normal((20, 1024), dtype=np.float32) * np.float32(0.02)
+    packed = qz.quantize(t, w)
+    assert packed.shape == (20, g.row_bytes(t, 1024)) and packed.dtype == np.uint8
+    deq = oracle.dequantize(int(t), packed)
+    step = {"Q8_0": 1 / 127, "Q4_0": 1 / 8, "Q4_K": 1 / 15, "Q6_K": 1 / 32}[name]
+    assert np.abs(deq - w).max() <= np.abs(w).max() * step * 1.1
+    tiled = qz.synthetic_weights(t, 2500, 512, band=1024)
+    assert tiled.shape == (2500, g.row_bytes(t, 512)) and np.array_equal(tiled[:1024][:452], tiled[2048:2500])
