@@ -111,9 +111,8 @@ int b200q_weight_upload(int device, int ggml_type, int64_t n_rows, int64_t k, co
 
     auto w = std::make_shared<Weight>();
     w->type = ggml_type, w->device = device, w->n = n_rows, w->k = k;
-    const int tk = fmt_tk(ggml_type);
-    w->rt = (n_rows + 15) / 16;
-    w->kt = (k + tk - 1) / tk;
+    w->rt = (n_rows + kTileRows - 1) / kTileRows;
+    w->kt = (k + kTileK - 1) / kTileK;
     w->bytes = w->rt * w->kt * (int64_t)fmt_tile_bytes(ggml_type);
     B200Q_CUDA(cudaMalloc(&w->tiles, (size_t)w->bytes));
     cudaError_t e = cudaMalloc(&w->status, sizeof(int));
@@ -207,6 +206,7 @@ int b200q_dense(b200q_weight_t h, const void *x_dev, int x_dtype, int64_t m, con
                 float *y_dev, int64_t y_ld, void *stream) {
     auto w = find(h);
     if (!w) return fail(B200Q_EHANDLE, "dense: unknown handle");
+    if (m == 0) return B200Q_OK;  // empty batch: nothing to read or write
     if (!x_dev || !y_dev) return fail(B200Q_EINVAL, "dense: null x or y");
     if (x_dtype != B200Q_F32 && x_dtype != B200Q_BF16) return fail(B200Q_EINVAL, "dense: x dtype must be f32 or bf16");
     if (activation < B200Q_ACT_NONE || activation > B200Q_ACT_TANH) return fail(B200Q_EINVAL, "dense: bad activation");

@@ -43,6 +43,7 @@
 
 #include <algorithm>
 #include <climits>
+#include <cmath>
 #include <cstdlib>
 #include <map>
 #include <mutex>
@@ -60,17 +61,39 @@ struct GemvParams {
     float *y;
     int *status;
     int64_t n, k, y_ld;
-    int64_t rt, kt;
+    int64_t rt, kt;  // row tiles (16 rows) and k tiles (256 values) of the weight
     int m, x_dtype, act;
-    int ktc;     // k tiles per staged x chunk
-    int splits;  // CTAs per cluster; split s owns k tiles [s*kts, (s+1)*kts)
+    int splits;     // CTAs per cluster (power of two); split s owns k tiles [s*kts, (s+1)*kts)
+    int split_shift;
     int kts;
-    int nclusters;
-    int depth;   // ring slots per warp
-    int maxnj;   // upper bound on row tiles per warp
+    int nclusters;  // cluster c owns rows_q row tiles, the first rows_r clusters one more
+    int rows_q, rows_r;
+    int kp;         // k parts per row tile inside a CTA: unit = (row tile, k part)
+    int ktp;        // k tiles per part
+    int depth;      // ring slots per warp
+    int tps;        // tiles per ring slot (one TMA copy)
+    int maxunits;   // upper bound on units per CTA (sizes the partial-sum area)
 };
 
 constexpr int kSpinLimit = 1 << 22;
+
+#ifdef B200Q_TRACE
+// Diagnostic build only: per-CTA timestamps (ns) at five points of the kernel.
+__device__ unsigned long long *g_trace = nullptr;
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define B200Q_TRACE_POINT(i)                                                              \
+    do {                                                                                  \
+        if (g_trace != nullptr && threadIdx.x == 0) g_trace[blockIdx.x * 8 + (i)] = now_ns(); \
+    } while (0)
+#else
+#define B200Q_TRACE_POINT(i) \
+    do {                     \
+    } while (0)
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -173,8 +196,7 @@ struct XBase {
 };
 
 template <int NB>
-__device__ __forceinline__ void xcols_for_tile(XCols<NB> &xc, const XBase<NB> &xb, int chunk0, int sub0, int t) {
-    const int a = (t & 1) * 32, b = (t >> 1) * 64;
+__device__ __forceinline__ void xcols_for_tile(XCols<NB> &xc, const XBase<NB> &xb, int chunk0, int sub0, int a, int b) {
 #pragma unroll
     for (int nb = 0; nb < NB; nb++) {
         const uint32_t base = xb.x[nb] + chunk0 * 16;
@@ -199,45 +221,80 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
 }
 
 // ---------------------------------------------------------------------------------------
-// Q4_0 : tile = 16 rows x 512 k, 9 loads per lane.
+// Tile functions.  `tile` is the shared-memory address of a 16-row x 256-value tile, `lane`
+// = 4g + t.  Each adds the tile's contribution for rows g, g+8 and the lane's batch columns
+// to two independent accumulator sets (shorter HMMA dependency chains).
 // ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+// Masks and exponent patterns of the nibble extraction, held in registers.  They are produced by
+// opaque moves so that the compiler keeps them resident instead of re-materialising two immediates
+// around every (w & mask) | magic, which then is a single LOP3.
+struct NibbleConsts {
+    uint32_t mask_lo, mask_hi, magic_1024, magic_64;
+};
+__device__ __forceinline__ NibbleConsts nibble_consts() {
+    NibbleConsts c;
+    asm volatile("mov.u32 %0, 0x000F000F;" : "=r"(c.mask_lo));
+    asm volatile("mov.u32 %0, 0x00F000F0;" : "=r"(c.mask_hi));
+    asm volatile("mov.u32 %0, 0x64006400;" : "=r"(c.magic_1024));
+    asm volatile("mov.u32 %0, 0x54005400;" : "=r"(c.magic_64));
+    return c;
+}
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {  // (a & b) | c
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// Nibble word -> four fp16 pairs scaled by the block scale (see the file header).
+__device__ __forceinline__ void nibbles_to_h2(const NibbleConsts &c, uint32_t w, uint32_t s_lo, uint32_t o_lo,
+                                              uint32_t s_hi, uint32_t o_hi, uint32_t &l0, uint32_t &l1, uint32_t &h0,
+                                              uint32_t &h1) {
+    const uint32_t w8 = w >> 8;
+    l0 = hfma2u(and_or(w, c.mask_lo, c.magic_1024), s_lo, o_lo);
+    l1 = hfma2u(and_or(w8, c.mask_lo, c.magic_1024), s_lo, o_lo);
+    h0 = hfma2u(and_or(w, c.mask_hi, c.magic_64), s_hi, o_hi);
+    h1 = hfma2u(and_or(w8, c.mask_hi, c.magic_64), s_hi, o_hi);
+}
+
+#define B200Q_WORD(v, wp, ww) ((wp) == 0 ? ((ww) == 0 ? (v).x : (v).y) : ((ww) == 0 ? (v).z : (v).w))
+
+// Q4_0: lane quarter = blocks 2t, 2t+1.
 template <int NB>
-__device__ __forceinline__ void tile_q4_0(uint32_t slot, const XCols<NB> &xc, float (&acc)[2][NB][4]) {
-    const uint4 sc = lds128(slot);
+__device__ __forceinline__ void tile_q4_0(uint32_t tile, int lane, const XCols<NB> &xc, const NibbleConsts &nc,
+                                          float (&acc)[2][NB][4]) {
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t sc = lds32(tile + g * 16 + t * 4), sc8 = lds32(tile + (g + 8) * 16 + t * 4);
 #pragma unroll
     for (int nb = 0; nb < NB; nb++) {  // offset term: sum_b d_b * (-8 * sum(x in block b))
-        const uint2 bh = lds64(xc.shi[nb]), bl = lds64(xc.slo[nb]);
-        mma16816(acc[0][nb], sc.x, sc.z, sc.y, sc.w, bh.x, bh.y);
-        mma16816(acc[1][nb], sc.x, sc.z, sc.y, sc.w, bl.x, bl.y);
+        mma16816(acc[0][nb], sc, sc8, 0u, 0u, lds32(xc.shi[nb]), 0u);
+        mma16816(acc[1][nb], sc, sc8, 0u, 0u, lds32(xc.slo[nb]), 0u);
     }
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const uint32_t pg = i < 2 ? sc.x : sc.y, pg8 = i < 2 ? sc.z : sc.w;
-        const uint32_t dg = (i & 1) ? bcast_hi(pg) : bcast_lo(pg), dg8 = (i & 1) ? bcast_hi(pg8) : bcast_lo(pg8);
+    for (int bp = 0; bp < 2; bp++) {
+        const uint32_t dg = bp ? bcast_hi(sc) : bcast_lo(sc), dg8 = bp ? bcast_hi(sc8) : bcast_lo(sc8);
         const uint32_t olo = hmul2u(dg, H2_N1024), ohi = hmul2u(dg, H2_N64);
         const uint32_t olo8 = hmul2u(dg8, H2_N1024), ohi8 = hmul2u(dg8, H2_N64);
-        const uint4 qa = lds128(slot + (1 + 2 * i) * 512), qb = lds128(slot + (2 + 2 * i) * 512);
+        const uint4 qa = lds128(tile + 256 + (2 * bp) * 512 + lane * 16);
+        const uint4 qb = lds128(tile + 256 + (2 * bp + 1) * 512 + lane * 16);
 #pragma unroll
         for (int wp = 0; wp < 2; wp++) {
             uint4 blo[NB], bhi[NB];
 #pragma unroll
             for (int nb = 0; nb < NB; nb++) {
-                blo[nb] = lds_chunk(xc, nb, 4 * i + wp);
-                bhi[nb] = lds_chunk(xc, nb, 4 * i + 2 + wp);
+                blo[nb] = lds_chunk(xc, nb, 4 * bp + wp);
+                bhi[nb] = lds_chunk(xc, nb, 4 * bp + 2 + wp);
             }
 #pragma unroll
             for (int ww = 0; ww < 2; ww++) {
-                const uint32_t wa = wp == 0 ? (ww == 0 ? qa.x : qa.y) : (ww == 0 ? qa.z : qa.w);
-                const uint32_t wb = wp == 0 ? (ww == 0 ? qb.x : qb.y) : (ww == 0 ? qb.z : qb.w);
-                const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
-                const uint32_t l0 = hfma2u((wa & 0x000F000Fu) | MAGIC_1024, dg, olo);
-                const uint32_t l1 = hfma2u((wb & 0x000F000Fu) | MAGIC_1024, dg8, olo8);
-                const uint32_t l2 = hfma2u((wa8 & 0x000F000Fu) | MAGIC_1024, dg, olo);
-                const uint32_t l3 = hfma2u((wb8 & 0x000F000Fu) | MAGIC_1024, dg8, olo8);
-                const uint32_t h0 = hfma2u((wa & 0x00F000F0u) | MAGIC_64, dg, ohi);
-                const uint32_t h1 = hfma2u((wb & 0x00F000F0u) | MAGIC_64, dg8, ohi8);
-                const uint32_t h2 = hfma2u((wa8 & 0x00F000F0u) | MAGIC_64, dg, ohi);
-                const uint32_t h3 = hfma2u((wb8 & 0x00F000F0u) | MAGIC_64, dg8, ohi8);
+                uint32_t l0, l1, l2, l3, h0, h1, h2, h3;
+                nibbles_to_h2(nc, B200Q_WORD(qa, wp, ww), dg, olo, dg, ohi, l0, l2, h0, h2);
+                nibbles_to_h2(nc, B200Q_WORD(qb, wp, ww), dg8, olo8, dg8, ohi8, l1, l3, h1, h3);
 #pragma unroll
                 for (int nb = 0; nb < NB; nb++) {
                     mma16816(acc[0][nb], l0, l1, l2, l3, ww == 0 ? blo[nb].x : blo[nb].z, ww == 0 ? blo[nb].y : blo[nb].w);
@@ -248,29 +305,26 @@ __device__ __forceinline__ void tile_q4_0(uint32_t slot, const XCols<NB> &xc, fl
     }
 }
 
-// ---------------------------------------------------------------------------------------
-// Q8_0 : tile = 16 rows x 512 k, 17 loads per lane.
-// ---------------------------------------------------------------------------------------
+// Q8_0: lane quarter = blocks 2t, 2t+1.
 template <int NB>
-__device__ __forceinline__ void tile_q8_0(uint32_t slot, const XCols<NB> &xc, float (&acc)[2][NB][4]) {
-    const uint4 sc = lds128(slot);
+__device__ __forceinline__ void tile_q8_0(uint32_t tile, int lane, const XCols<NB> &xc, float (&acc)[2][NB][4]) {
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t sc = lds32(tile + g * 16 + t * 4), sc8 = lds32(tile + (g + 8) * 16 + t * 4);
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const uint32_t pg = i < 2 ? sc.x : sc.y, pg8 = i < 2 ? sc.z : sc.w;
-        const uint32_t dg = (i & 1) ? bcast_hi(pg) : bcast_lo(pg), dg8 = (i & 1) ? bcast_hi(pg8) : bcast_lo(pg8);
+    for (int bp = 0; bp < 2; bp++) {
+        const uint32_t dg = bp ? bcast_hi(sc) : bcast_lo(sc), dg8 = bp ? bcast_hi(sc8) : bcast_lo(sc8);
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            const int j = 1 + 2 * (2 * i + h);
-            const uint4 qa = lds128(slot + j * 512), qb = lds128(slot + (j + 1) * 512);
+            const uint4 qa = lds128(tile + 256 + (2 * (2 * bp + h)) * 512 + lane * 16);
+            const uint4 qb = lds128(tile + 256 + (2 * (2 * bp + h) + 1) * 512 + lane * 16);
 #pragma unroll
             for (int wp = 0; wp < 2; wp++) {
                 uint4 b[NB];
 #pragma unroll
-                for (int nb = 0; nb < NB; nb++) b[nb] = lds_chunk(xc, nb, 4 * i + 2 * h + wp);
+                for (int nb = 0; nb < NB; nb++) b[nb] = lds_chunk(xc, nb, 4 * bp + 2 * h + wp);
 #pragma unroll
                 for (int ww = 0; ww < 2; ww++) {
-                    const uint32_t wa = (wp == 0 ? (ww == 0 ? qa.x : qa.y) : (ww == 0 ? qa.z : qa.w)) ^ 0x80808080u;
-                    const uint32_t wb = (wp == 0 ? (ww == 0 ? qb.x : qb.y) : (ww == 0 ? qb.z : qb.w)) ^ 0x80808080u;
+                    const uint32_t wa = B200Q_WORD(qa, wp, ww) ^ 0x80808080u, wb = B200Q_WORD(qb, wp, ww) ^ 0x80808080u;
                     const uint32_t a0 = hmul2u(hsub2u(bytes_to_h2(wa, SEL01), H2_1152), dg);
                     const uint32_t a1 = hmul2u(hsub2u(bytes_to_h2(wb, SEL01), H2_1152), dg8);
                     const uint32_t a2 = hmul2u(hsub2u(bytes_to_h2(wa, SEL23), H2_1152), dg);
@@ -284,68 +338,56 @@ __device__ __forceinline__ void tile_q8_0(uint32_t slot, const XCols<NB> &xc, fl
     }
 }
 
-// ---------------------------------------------------------------------------------------
-// Q4_K : tile = 16 rows x 1024 k (4 super-blocks, one per quad lane), 18 loads per lane.
-// ---------------------------------------------------------------------------------------
-// Header (d, dmin, scales[12]) -> fp16 pairs ds[j/2] = d*sc_j and cm[j/2] = dmin*m_j.
-__device__ __forceinline__ void q4k_header(const uint4 &h, uint32_t (&ds)[4], uint32_t (&cm)[4]) {
+// Q4_K header (d, dmin, scales[12]) of one row -> fp16 pairs for the lane's sub-blocks 2t, 2t+1:
+// ds = (d*sc_2t, d*sc_2t+1), cm = (dmin*m_2t, dmin*m_2t+1).
+__device__ __forceinline__ void q4k_header(const uint4 &h, int t, uint32_t &ds, uint32_t &cm) {
     const uint32_t d2 = bcast_lo(h.x), dmin2 = bcast_hi(h.x);
-    const uint32_t sc0 = h.y & 0x3F3F3F3Fu, m0 = h.z & 0x3F3F3F3Fu;
-    const uint32_t sc1 = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
-    const uint32_t m1 = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
-    ds[0] = hmul2u(hsub2u(bytes_to_h2(sc0, SEL01), H2_1024), d2);
-    ds[1] = hmul2u(hsub2u(bytes_to_h2(sc0, SEL23), H2_1024), d2);
-    ds[2] = hmul2u(hsub2u(bytes_to_h2(sc1, SEL01), H2_1024), d2);
-    ds[3] = hmul2u(hsub2u(bytes_to_h2(sc1, SEL23), H2_1024), d2);
-    cm[0] = hmul2u(hsub2u(bytes_to_h2(m0, SEL01), H2_1024), dmin2);
-    cm[1] = hmul2u(hsub2u(bytes_to_h2(m0, SEL23), H2_1024), dmin2);
-    cm[2] = hmul2u(hsub2u(bytes_to_h2(m1, SEL01), H2_1024), dmin2);
-    cm[3] = hmul2u(hsub2u(bytes_to_h2(m1, SEL23), H2_1024), dmin2);
+    uint32_t sc, mn;
+    if (t < 2) {  // sub-blocks 0..3: low six bits of bytes 0..3 / 4..7
+        sc = h.y & 0x3F3F3F3Fu;
+        mn = h.z & 0x3F3F3F3Fu;
+    } else {      // sub-blocks 4..7: nibbles of bytes 8..11 plus the top two bits of bytes 0..7
+        sc = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
+        mn = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
+    }
+    const uint32_t sel = (t & 1) ? SEL23 : SEL01;
+    ds = hmul2u(hsub2u(bytes_to_h2(sc, sel), H2_1024), d2);
+    cm = hmul2u(hsub2u(bytes_to_h2(mn, sel), H2_1024), dmin2);
 }
 
+// Q4_K: lane quarter = group t of the super-block (low nibbles: sub-block 2t, high: 2t+1).
 template <int NB>
-__device__ __forceinline__ void tile_q4_k(uint32_t slot, const XCols<NB> &xc, float (&acc)[2][NB][4]) {
-    uint32_t dsA[4], cmA[4], dsB[4], cmB[4];
-    q4k_header(lds128(slot), dsA, cmA);
-    q4k_header(lds128(slot + 512), dsB, cmB);
+__device__ __forceinline__ void tile_q4_k(uint32_t tile, int lane, const XCols<NB> &xc, const NibbleConsts &nc,
+                                          float (&acc)[2][NB][4]) {
+    const int g = lane >> 2, t = lane & 3;
+    uint32_t ds, cm, ds8, cm8;
+    q4k_header(lds128(tile + g * 16), t, ds, cm);
+    q4k_header(lds128(tile + (g + 8) * 16), t, ds8, cm8);
 #pragma unroll
     for (int nb = 0; nb < NB; nb++) {  // offset term: sum_j (dmin*m_j) * (-sum(x in sub-block j))
-#pragma unroll
-        for (int q = 0; q < 2; q++) {
-            const uint2 bh = lds64(xc.shi[nb] + 8 * q), bl = lds64(xc.slo[nb] + 8 * q);
-            mma16816(acc[0][nb], cmA[2 * q], cmB[2 * q], cmA[2 * q + 1], cmB[2 * q + 1], bh.x, bh.y);
-            mma16816(acc[1][nb], cmA[2 * q], cmB[2 * q], cmA[2 * q + 1], cmB[2 * q + 1], bl.x, bl.y);
-        }
+        mma16816(acc[0][nb], cm, cm8, 0u, 0u, lds32(xc.shi[nb]), 0u);
+        mma16816(acc[1][nb], cm, cm8, 0u, 0u, lds32(xc.slo[nb]), 0u);
     }
+    const uint32_t sl = bcast_lo(ds), sh = bcast_hi(ds), sl8 = bcast_lo(ds8), sh8 = bcast_hi(ds8);
+    const uint32_t olo = hmul2u(sl, H2_N1024), ohi = hmul2u(sh, H2_N64);
+    const uint32_t olo8 = hmul2u(sl8, H2_N1024), ohi8 = hmul2u(sh8, H2_N64);
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const int G = i >> 1, hf = i & 1;
-        // low nibbles: sub-block 2G (low half of pair G); high nibbles: sub-block 2G+1.
-        const uint32_t sl = bcast_lo(dsA[G]), sh = bcast_hi(dsA[G]), sl8 = bcast_lo(dsB[G]), sh8 = bcast_hi(dsB[G]);
-        const uint32_t olo = hmul2u(sl, H2_N1024), ohi = hmul2u(sh, H2_N64);
-        const uint32_t olo8 = hmul2u(sl8, H2_N1024), ohi8 = hmul2u(sh8, H2_N64);
-        const uint4 qa = lds128(slot + (2 + 2 * i) * 512), qb = lds128(slot + (3 + 2 * i) * 512);
+    for (int i = 0; i < 2; i++) {
+        const uint4 qa = lds128(tile + 256 + (2 * i) * 512 + lane * 16);
+        const uint4 qb = lds128(tile + 256 + (2 * i + 1) * 512 + lane * 16);
 #pragma unroll
         for (int wp = 0; wp < 2; wp++) {
             uint4 blo[NB], bhi[NB];
 #pragma unroll
             for (int nb = 0; nb < NB; nb++) {
-                blo[nb] = lds_chunk(xc, nb, 8 * G + 2 * hf + wp);
-                bhi[nb] = lds_chunk(xc, nb, 8 * G + 2 * hf + 4 + wp);
+                blo[nb] = lds_chunk(xc, nb, 2 * i + wp);
+                bhi[nb] = lds_chunk(xc, nb, 4 + 2 * i + wp);
             }
 #pragma unroll
             for (int ww = 0; ww < 2; ww++) {
-                const uint32_t wa = wp == 0 ? (ww == 0 ? qa.x : qa.y) : (ww == 0 ? qa.z : qa.w);
-                const uint32_t wb = wp == 0 ? (ww == 0 ? qb.x : qb.y) : (ww == 0 ? qb.z : qb.w);
-                const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
-                const uint32_t l0 = hfma2u((wa & 0x000F000Fu) | MAGIC_1024, sl, olo);
-                const uint32_t l1 = hfma2u((wb & 0x000F000Fu) | MAGIC_1024, sl8, olo8);
-                const uint32_t l2 = hfma2u((wa8 & 0x000F000Fu) | MAGIC_1024, sl, olo);
-                const uint32_t l3 = hfma2u((wb8 & 0x000F000Fu) | MAGIC_1024, sl8, olo8);
-                const uint32_t h0 = hfma2u((wa & 0x00F000F0u) | MAGIC_64, sh, ohi);
-                const uint32_t h1 = hfma2u((wb & 0x00F000F0u) | MAGIC_64, sh8, ohi8);
-                const uint32_t h2 = hfma2u((wa8 & 0x00F000F0u) | MAGIC_64, sh, ohi);
-                const uint32_t h3 = hfma2u((wb8 & 0x00F000F0u) | MAGIC_64, sh8, ohi8);
+                uint32_t l0, l1, l2, l3, h0, h1, h2, h3;
+                nibbles_to_h2(nc, B200Q_WORD(qa, wp, ww), sl, olo, sh, ohi, l0, l2, h0, h2);
+                nibbles_to_h2(nc, B200Q_WORD(qb, wp, ww), sl8, olo8, sh8, ohi8, l1, l3, h1, h3);
 #pragma unroll
                 for (int nb = 0; nb < NB; nb++) {
                     mma16816(acc[0][nb], l0, l1, l2, l3, ww == 0 ? blo[nb].x : blo[nb].z, ww == 0 ? blo[nb].y : blo[nb].w);
@@ -356,84 +398,67 @@ __device__ __forceinline__ void tile_q4_k(uint32_t slot, const XCols<NB> &xc, fl
     }
 }
 
-// ---------------------------------------------------------------------------------------
-// Q6_K : tile = 16 rows x 1024 k (4 super-blocks), 26 loads + one 4-byte load per lane.
-// ---------------------------------------------------------------------------------------
-// int8 scales[16] and d -> fp16 pairs ds[s/2] = d * sc_s.
-__device__ __forceinline__ void q6k_scales(const uint4 &s, uint32_t d2, uint32_t (&ds)[8]) {
-    const uint32_t w[4] = {s.x ^ 0x80808080u, s.y ^ 0x80808080u, s.z ^ 0x80808080u, s.w ^ 0x80808080u};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        ds[2 * i] = hmul2u(hsub2u(bytes_to_h2(w[i], SEL01), H2_1152), d2);
-        ds[2 * i + 1] = hmul2u(hsub2u(bytes_to_h2(w[i], SEL23), H2_1152), d2);
-    }
+// Q6_K scales of the lane's four sub-blocks (8n + lh + 2c, c = 0..3) times d, as fp16 pairs
+// p01 = (c0, c1), p23 = (c2, c3).  `s` holds int8 scales 8n .. 8n+7 of the row.
+__device__ __forceinline__ void q6k_scales(const uint2 &s, int lh, uint32_t d2, uint32_t &p01, uint32_t &p23) {
+    const uint32_t sel = lh ? 0x5341u : 0x5240u;  // bytes (lh, 2+lh) interleaved with the 0x64 magic
+    p01 = hmul2u(hsub2u(__byte_perm(s.x ^ 0x80808080u, BYTES_64, sel), H2_1152), d2);
+    p23 = hmul2u(hsub2u(__byte_perm(s.y ^ 0x80808080u, BYTES_64, sel), H2_1152), d2);
 }
 
+// Q6_K: lane t = (n = t>>1, lh = t&1) owns values 128n + 32c + 16lh + 0..15, c = 0..3.
 template <int NB>
-__device__ __forceinline__ void tile_q6_k(uint32_t slot, uint32_t slot_tail, const XCols<NB> &xc,
-                                          float (&acc)[2][NB][4]) {
-    uint32_t dsA[8], dsB[8];
-    const uint32_t tail = lds32(slot_tail);  // fp16 d of row g | row g+8
-    q6k_scales(lds128(slot), bcast_lo(tail), dsA);
-    q6k_scales(lds128(slot + 512), bcast_hi(tail), dsB);
+__device__ __forceinline__ void tile_q6_k(uint32_t tile, int lane, const XCols<NB> &xc, float (&acc)[2][NB][4]) {
+    const int g = lane >> 2, t = lane & 3, n = t >> 1, lh = t & 1;
+    const uint32_t dg = lds16(tile + 3328 + g * 2), dg8 = lds16(tile + 3328 + (g + 8) * 2);
+    uint32_t p01, p23, p01_8, p23_8;
+    q6k_scales(lds64(tile + g * 16 + 8 * n), lh, bcast_lo(dg), p01, p23);
+    q6k_scales(lds64(tile + (g + 8) * 16 + 8 * n), lh, bcast_lo(dg8), p01_8, p23_8);
 #pragma unroll
     for (int nb = 0; nb < NB; nb++) {  // offset term: sum_s (d*sc_s) * (-32 * sum(x in sub-block s))
-#pragma unroll
-        for (int q = 0; q < 4; q++) {
-            const uint2 bh = lds64(xc.shi[nb] + 8 * q), bl = lds64(xc.slo[nb] + 8 * q);
-            mma16816(acc[0][nb], dsA[2 * q], dsB[2 * q], dsA[2 * q + 1], dsB[2 * q + 1], bh.x, bh.y);
-            mma16816(acc[1][nb], dsA[2 * q], dsB[2 * q], dsA[2 * q + 1], dsB[2 * q + 1], bl.x, bl.y);
-        }
+        const uint2 bh = lds64(xc.shi[nb]), bl = lds64(xc.slo[nb]);
+        mma16816(acc[0][nb], p01, p01_8, p23, p23_8, bh.x, bh.y);
+        mma16816(acc[1][nb], p01, p01_8, p23, p23_8, bl.x, bl.y);
     }
+    const uint4 la = lds128(tile + 256 + 0 * 512 + lane * 16), la8 = lds128(tile + 256 + 1 * 512 + lane * 16);
+    const uint4 lb = lds128(tile + 256 + 2 * 512 + lane * 16), lb8 = lds128(tile + 256 + 3 * 512 + lane * 16);
+    const uint4 hh = lds128(tile + 256 + 4 * 512 + lane * 16), hh8 = lds128(tile + 256 + 5 * 512 + lane * 16);
+    uint32_t s[4], s8[4], o[4], o8[4];
+    s[0] = bcast_lo(p01), s[1] = bcast_hi(p01), s[2] = bcast_lo(p23), s[3] = bcast_hi(p23);
+    s8[0] = bcast_lo(p01_8), s8[1] = bcast_hi(p01_8), s8[2] = bcast_lo(p23_8), s8[3] = bcast_hi(p23_8);
 #pragma unroll
-    for (int gr = 0; gr < 4; gr++) {
-        const int n = gr >> 1, lh = gr & 1, j0 = 2 + 6 * gr;
-        const uint4 la = lds128(slot + j0 * 512), la8 = lds128(slot + (j0 + 1) * 512), lb = lds128(slot + (j0 + 2) * 512),
-                    lb8 = lds128(slot + (j0 + 3) * 512), hh = lds128(slot + (j0 + 4) * 512),
-                    hh8 = lds128(slot + (j0 + 5) * 512);
-        uint32_t s[4], s8[4], o[4], o8[4];
+    for (int c = 0; c < 4; c++) o[c] = hmul2u(s[c], H2_N1024), o8[c] = hmul2u(s8[c], H2_N1024);
 #pragma unroll
-        for (int c = 0; c < 4; c++) {  // code c uses scale 8n + lh + 2c = half lh of pair 4n + c
-            s[c] = lh ? bcast_hi(dsA[4 * n + c]) : bcast_lo(dsA[4 * n + c]);
-            s8[c] = lh ? bcast_hi(dsB[4 * n + c]) : bcast_lo(dsB[4 * n + c]);
-            o[c] = hmul2u(s[c], H2_N1024);
-            o8[c] = hmul2u(s8[c], H2_N1024);
-        }
+    for (int wp = 0; wp < 2; wp++) {
+        uint4 b[4][NB];
 #pragma unroll
-        for (int wp = 0; wp < 2; wp++) {
-            uint4 b[4][NB];
+        for (int c = 0; c < 4; c++)
 #pragma unroll
-            for (int c = 0; c < 4; c++)
+            for (int nb = 0; nb < NB; nb++) b[c][nb] = lds_chunk(xc, nb, 4 * c + wp);
 #pragma unroll
-                for (int nb = 0; nb < NB; nb++) b[c][nb] = lds_chunk(xc, nb, 16 * n + 2 * lh + 4 * c + wp);
+        for (int ww = 0; ww < 2; ww++) {
+            const uint32_t a = B200Q_WORD(la, wp, ww), a8 = B200Q_WORD(la8, wp, ww);
+            const uint32_t bq = B200Q_WORD(lb, wp, ww), bq8 = B200Q_WORD(lb8, wp, ww);
+            const uint32_t h = B200Q_WORD(hh, wp, ww), h8 = B200Q_WORD(hh8, wp, ww);
+            uint32_t code[4], code8[4];
+            code[0] = (a & 0x0F0F0F0Fu) | ((h << 4) & 0x30303030u);
+            code[1] = (bq & 0x0F0F0F0Fu) | ((h << 2) & 0x30303030u);
+            code[2] = ((a >> 4) & 0x0F0F0F0Fu) | (h & 0x30303030u);
+            code[3] = ((bq >> 4) & 0x0F0F0F0Fu) | ((h >> 2) & 0x30303030u);
+            code8[0] = (a8 & 0x0F0F0F0Fu) | ((h8 << 4) & 0x30303030u);
+            code8[1] = (bq8 & 0x0F0F0F0Fu) | ((h8 << 2) & 0x30303030u);
+            code8[2] = ((a8 >> 4) & 0x0F0F0F0Fu) | (h8 & 0x30303030u);
+            code8[3] = ((bq8 >> 4) & 0x0F0F0F0Fu) | ((h8 >> 2) & 0x30303030u);
 #pragma unroll
-            for (int ww = 0; ww < 2; ww++) {
-                const uint32_t a = wp == 0 ? (ww == 0 ? la.x : la.y) : (ww == 0 ? la.z : la.w);
-                const uint32_t a8 = wp == 0 ? (ww == 0 ? la8.x : la8.y) : (ww == 0 ? la8.z : la8.w);
-                const uint32_t bq = wp == 0 ? (ww == 0 ? lb.x : lb.y) : (ww == 0 ? lb.z : lb.w);
-                const uint32_t bq8 = wp == 0 ? (ww == 0 ? lb8.x : lb8.y) : (ww == 0 ? lb8.z : lb8.w);
-                const uint32_t h = wp == 0 ? (ww == 0 ? hh.x : hh.y) : (ww == 0 ? hh.z : hh.w);
-                const uint32_t h8 = wp == 0 ? (ww == 0 ? hh8.x : hh8.y) : (ww == 0 ? hh8.z : hh8.w);
-                uint32_t code[4], code8[4];
-                code[0] = (a & 0x0F0F0F0Fu) | ((h << 4) & 0x30303030u);
-                code[1] = (bq & 0x0F0F0F0Fu) | ((h << 2) & 0x30303030u);
-                code[2] = ((a >> 4) & 0x0F0F0F0Fu) | (h & 0x30303030u);
-                code[3] = ((bq >> 4) & 0x0F0F0F0Fu) | ((h >> 2) & 0x30303030u);
-                code8[0] = (a8 & 0x0F0F0F0Fu) | ((h8 << 4) & 0x30303030u);
-                code8[1] = (bq8 & 0x0F0F0F0Fu) | ((h8 << 2) & 0x30303030u);
-                code8[2] = ((a8 >> 4) & 0x0F0F0F0Fu) | (h8 & 0x30303030u);
-                code8[3] = ((bq8 >> 4) & 0x0F0F0F0Fu) | ((h8 >> 2) & 0x30303030u);
+            for (int c = 0; c < 4; c++) {
+                const uint32_t a0 = hfma2u(bytes_to_h2(code[c], SEL01), s[c], o[c]);
+                const uint32_t a1 = hfma2u(bytes_to_h2(code8[c], SEL01), s8[c], o8[c]);
+                const uint32_t a2 = hfma2u(bytes_to_h2(code[c], SEL23), s[c], o[c]);
+                const uint32_t a3 = hfma2u(bytes_to_h2(code8[c], SEL23), s8[c], o8[c]);
 #pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    const uint32_t a0 = hfma2u(bytes_to_h2(code[c], SEL01), s[c], o[c]);
-                    const uint32_t a1 = hfma2u(bytes_to_h2(code8[c], SEL01), s8[c], o8[c]);
-                    const uint32_t a2 = hfma2u(bytes_to_h2(code[c], SEL23), s[c], o[c]);
-                    const uint32_t a3 = hfma2u(bytes_to_h2(code8[c], SEL23), s8[c], o8[c]);
-#pragma unroll
-                    for (int nb = 0; nb < NB; nb++)
-                        mma16816(acc[c & 1][nb], a0, a1, a2, a3, ww == 0 ? b[c][nb].x : b[c][nb].z,
-                                 ww == 0 ? b[c][nb].y : b[c][nb].w);
-                }
+                for (int nb = 0; nb < NB; nb++)
+                    mma16816(acc[c & 1][nb], a0, a1, a2, a3, ww == 0 ? b[c][nb].x : b[c][nb].z,
+                             ww == 0 ? b[c][nb].y : b[c][nb].w);
             }
         }
     }
@@ -449,87 +474,122 @@ __device__ __forceinline__ uint32_t f2h2_sat(float lo, float hi) {
     return d;
 }
 
+// One 8-value group of one column: convert to fp16, store swizzled, contribute to the aux sums.
+template <int TYPE>
+__device__ __forceinline__ void stage_group(const float (&v)[8], int col, int gi, int xs_stride, int ns, __half *xs,
+                                            __half *shi, __half *slo) {
+    using F = Fmt<TYPE>;
+    uint4 out;
+    if constexpr (F::PERM4) {
+        out.x = f2h2_sat(v[0], v[2]), out.y = f2h2_sat(v[1], v[3]);
+        out.z = f2h2_sat(v[4], v[6]), out.w = f2h2_sat(v[5], v[7]);
+    } else {
+        out.x = f2h2_sat(v[0], v[1]), out.y = f2h2_sat(v[2], v[3]);
+        out.z = f2h2_sat(v[4], v[5]), out.w = f2h2_sat(v[6], v[7]);
+    }
+    // Bank swizzle of the 16-byte chunk index (32 chunks per tile): the four lanes of a quad read
+    // chunks 8 apart (16 apart for Q6_K), so bits 1-2 (bit 2) are XOR-ed with the lane's quarter.
+    const int swz = TYPE == kQ6_K ? ((gi >> 4) & 1) << 2 : ((gi >> 3) & 3) << 1;
+    *reinterpret_cast<uint4 *>(xs + col * xs_stride + ((gi ^ swz) << 3)) = out;
+    if constexpr (F::SUB != 0) {
+        // Sums are taken over the rounded values the MMAs will see, so the offset cancels exactly.
+        const uint32_t w[4] = {out.x, out.y, out.z, out.w};
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+            sum += f.x + f.y;
+        }
+        constexpr float OFFSET = TYPE == kQ4_0 ? 8.0f : TYPE == kQ4_K ? 1.0f : 32.0f;
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        if constexpr (F::SUB == 32) sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        constexpr int GPS = F::SUB / 8;  // groups per sub-block
+        if ((gi & (GPS - 1)) == 0) {
+            const float sv = -OFFSET * sum;
+            const __half hi = __float2half_rn(sv);
+            const __half lo = __float2half_rn(sv - __half2float(hi));
+            int pos = gi / GPS;  // natural sub-block index inside the staged slice
+            if constexpr (TYPE == kQ6_K) {
+                // lane t = 2n + lh reads its four sub-blocks (8n + lh + 2c) as one 8-byte load
+                const int sb = pos & 15;
+                pos = (pos & ~15) | ((((sb >> 3) << 1) | (sb & 1)) << 2) | ((sb >> 1) & 3);
+            }
+            shi[col * ns + pos] = hi;
+            slo[col * ns + pos] = lo;
+        }
+    }
+}
+
+// Stages x[0..m, k0 .. k0+kc) as fp16 in shared memory.  Loads of up to eight batch columns are
+// issued together so that their latencies overlap.
 template <int TYPE>
 __device__ __forceinline__ void stage_x(const GemvParams &p, int64_t k0, int kc, int xs_stride, int ns, __half *xs,
                                         __half *shi, __half *slo) {
-    using F = Fmt<TYPE>;
-    const int gpc = kc >> 3;  // 8-value groups per column, a multiple of 64
-    const int total = p.m * gpc;
-    for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
-        const int col = idx / gpc, gi = idx - col * gpc;
+    constexpr int CB = 8;
+    const int gpc = kc >> 3;  // 8-value groups per column, a multiple of 32
+    for (int gi = threadIdx.x; gi < gpc; gi += blockDim.x) {
         const int64_t k = k0 + (int64_t)gi * 8;
-        float v[8];
-        if (k < p.k) {
+        const bool in_range = k < p.k;
+        for (int c0 = 0; c0 < p.m; c0 += CB) {
             if (p.x_dtype == B200Q_F32) {
-                const float4 *src = reinterpret_cast<const float4 *>(static_cast<const float *>(p.x) + col * p.k + k);
-                const float4 a = __ldg(src), b = __ldg(src + 1);
-                v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
-            } else {
-                const uint4 r =
-                    __ldg(reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.x) + col * p.k + k));
-                const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+                float4 ra[CB], rb[CB];
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    v[2 * i] = __uint_as_float(w[i] << 16);
-                    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+                for (int c = 0; c < CB; c++) {
+                    if (in_range && c0 + c < p.m) {
+                        const float4 *src = reinterpret_cast<const float4 *>(static_cast<const float *>(p.x) + (int64_t)(c0 + c) * p.k + k);
+                        ra[c] = __ldg(src), rb[c] = __ldg(src + 1);
+                    } else {
+                        ra[c] = rb[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
                 }
-            }
-        } else {
 #pragma unroll
-            for (int i = 0; i < 8; i++) v[i] = 0.0f;
-        }
-        uint4 out;
-        if constexpr (F::PERM4) {
-            out.x = f2h2_sat(v[0], v[2]), out.y = f2h2_sat(v[1], v[3]);
-            out.z = f2h2_sat(v[4], v[6]), out.w = f2h2_sat(v[5], v[7]);
-        } else {
-            out.x = f2h2_sat(v[0], v[1]), out.y = f2h2_sat(v[2], v[3]);
-            out.z = f2h2_sat(v[4], v[5]), out.w = f2h2_sat(v[6], v[7]);
-        }
-        const int tq = ((gi << 3) & (F::TK - 1)) / (F::TK / 4);
-        *reinterpret_cast<uint4 *>(xs + col * xs_stride + ((gi ^ (2 * tq)) << 3)) = out;
-        if constexpr (F::SUB != 0) {
-            // Sums are taken over the rounded values the MMAs will see, so the offset cancels exactly.
-            const uint32_t w[4] = {out.x, out.y, out.z, out.w};
-            float sum = 0.0f;
+                for (int c = 0; c < CB; c++) {
+                    if (c0 + c < p.m) {
+                        const float v[8] = {ra[c].x, ra[c].y, ra[c].z, ra[c].w, rb[c].x, rb[c].y, rb[c].z, rb[c].w};
+                        stage_group<TYPE>(v, c0 + c, gi, xs_stride, ns, xs, shi, slo);
+                    }
+                }
+            } else {
+                uint4 r[CB];
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
-                sum += f.x + f.y;
-            }
-            constexpr float OFFSET = TYPE == kQ4_0 ? 8.0f : TYPE == kQ4_K ? 1.0f : 32.0f;
-            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-            if constexpr (F::SUB == 32) sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-            constexpr int GPS = F::SUB / 8;  // groups per sub-block
-            if ((gi & (GPS - 1)) == 0) {
-                const float s = -OFFSET * sum;
-                const __half hi = __float2half_rn(s);
-                const __half lo = __float2half_rn(s - __half2float(hi));
-                shi[col * ns + gi / GPS] = hi;
-                slo[col * ns + gi / GPS] = lo;
+                for (int c = 0; c < CB; c++) {
+                    if (in_range && c0 + c < p.m)
+                        r[c] = __ldg(reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.x) + (int64_t)(c0 + c) * p.k + k));
+                    else
+                        r[c] = make_uint4(0u, 0u, 0u, 0u);
+                }
+#pragma unroll
+                for (int c = 0; c < CB; c++) {
+                    if (c0 + c < p.m) {
+                        const uint32_t w[4] = {r[c].x, r[c].y, r[c].z, r[c].w};
+                        float v[8];
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            v[2 * i] = __uint_as_float(w[i] << 16);
+                            v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+                        }
+                        stage_group<TYPE>(v, c0 + c, gi, xs_stride, ns, xs, shi, slo);
+                    }
+                }
             }
         }
     }
 }
 
-// Walks one warp's tile sequence: x chunks (outer), the warp's row tiles (middle), k tiles (inner).
-struct TileWalk {
-    int64_t kt0;
-    int j, kl;
-};
-
 // Grid = nclusters x splits CTAs; the `splits` CTAs of a cluster hold the K slices of the same rows.
-// Cluster c owns row tiles [c*RT/nclusters, (c+1)*RT/nclusters); inside a CTA warp w takes every
-// nwarps-th of them.  Shared memory: staged x | aux sums | partial sums | tile rings | mbarriers.
+// Inside a CTA the work is cut into units = (row tile, k part); warp w takes units w, w + nwarps, ...
+// and streams each unit's tiles through its private ring of shared-memory slots.
+// Shared memory: staged x | aux sums | partial sums per unit | tile rings | mbarriers.
 template <int TYPE, int NB>
 __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
     using F = Fmt<TYPE>;
     extern __shared__ __align__(128) uint8_t smem[];
+    B200Q_TRACE_POINT(0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int nwarps = blockDim.x >> 5;
-    const int kc_max = p.ktc * F::TK;
-    const int xs_stride = kc_max + 8;
-    const int ns = F::SUB ? kc_max / F::SUB : 0;
+    const int kc = p.kts * F::TK;  // staged K slice (values)
+    const int xs_stride = kc + 8;
+    const int ns = F::SUB ? kc / F::SUB : 0;
     size_t off = 0;
     __half *xs = reinterpret_cast<__half *>(smem);
     off += (size_t)p.m * xs_stride * 2;
@@ -537,19 +597,21 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
     __half *slo = shi + (size_t)p.m * ns;
     off += (size_t)p.m * ns * 4;
     off = (off + 15) & ~(size_t)15;
-    float *red = reinterpret_cast<float *>(smem + off);  // [j][warp][nb][i][lane]
-    off += (size_t)p.maxnj * nwarps * NB * 128 * sizeof(float);
+    float *red = reinterpret_cast<float *>(smem + off);  // [unit][nb][i][lane]
+    off += (size_t)p.maxunits * NB * 128 * sizeof(float);
     off = (off + 127) & ~(size_t)127;
-    uint8_t *ring = smem + off + (size_t)warp * p.depth * F::TILE;
-    off += (size_t)nwarps * p.depth * F::TILE;
+    const uint32_t slot_bytes = p.tps * F::TILE;
+    uint8_t *ring = smem + off + (size_t)warp * p.depth * slot_bytes;
+    off += (size_t)nwarps * p.depth * slot_bytes;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + off) + warp * p.depth;
 
-    const int split = (int)(blockIdx.x % p.splits);
-    const int64_t cl = blockIdx.x / p.splits;
-    const int64_t r0 = cl * p.rt / p.nclusters, r1 = (cl + 1) * p.rt / p.nclusters;
-    const int64_t kt_begin = (int64_t)split * p.kts, kt_end = min(kt_begin + p.kts, p.kt);
-    const int nj = (kt_begin < kt_end && r0 + warp < r1) ? (int)((r1 - r0 - warp + nwarps - 1) / nwarps) : 0;
-    const int total = nj * (int)(kt_end > kt_begin ? kt_end - kt_begin : 0);  // tiles this warp consumes
+    const int split = (int)(blockIdx.x & (p.splits - 1));
+    const int cl = (int)(blockIdx.x >> p.split_shift);
+    const int r0 = cl * p.rows_q + min(cl, p.rows_r), r1 = r0 + p.rows_q + (cl < p.rows_r ? 1 : 0);
+    const int kt_begin = split * p.kts, kt_end = min(kt_begin + p.kts, (int)p.kt);
+    const int nrows = r1 - r0;
+    const int nunits = kt_begin < kt_end ? nrows * p.kp : 0;
+    const NibbleConsts nc = nibble_consts();
 
     const uint32_t ring_s = smem_u32(ring), bars_s = smem_u32(bars);
     if (lane == 0) {
@@ -559,126 +621,155 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
     }
     __syncwarp();
 
-    // Producer side (lane 0 of each warp): request the next tile of the warp's sequence into ring
-    // slot `pd`.  Sequence order: x chunks (outer), the warp's row tiles, k tiles of the chunk.
-    TileWalk pw{kt_begin, 0, 0};
-    int issued = 0, pd = 0;
-    auto issue_next = [&]() {
-        const int nkt = (int)min((int64_t)p.ktc, kt_end - pw.kt0);
-        const int64_t rt = r0 + warp + (int64_t)pw.j * nwarps;
-        const uint8_t *src = p.tiles + (rt * p.kt + pw.kt0 + pw.kl) * (int64_t)F::TILE;
-        mbar_expect_tx(bars_s + 8 * pd, F::TILE);
-        bulk_load(ring_s + pd * F::TILE, src, F::TILE, bars_s + 8 * pd);
-        issued++;
-        if (++pd == p.depth) pd = 0;
-        if (++pw.kl == nkt) {
-            pw.kl = 0;
-            if (++pw.j == nj) {
-                pw.j = 0;
-                pw.kt0 += p.ktc;
-            }
+    // Producer (lane 0 of each warp): walks the same (unit, k tile) sequence as the consumer,
+    // `depth` slots ahead.  Unit u = row * kp + part; (prow, ppart) track it without divisions.
+    int prow = 0, ppart = warp, pd = 0;
+    while (ppart >= p.kp) ppart -= p.kp, prow++;
+    int pk = kt_begin + ppart * p.ktp, pk1 = min(pk + p.ktp, kt_end);
+    auto producer_skip_empty = [&]() {
+        while (prow < nrows && pk >= pk1) {
+            ppart += nwarps;
+            while (ppart >= p.kp) ppart -= p.kp, prow++;
+            pk = kt_begin + ppart * p.ktp, pk1 = min(pk + p.ktp, kt_end);
         }
     };
+    if (nunits == 0) prow = nrows;
+    producer_skip_empty();
+    auto issue_next = [&]() {
+        const int nt = min(p.tps, pk1 - pk);
+        const uint8_t *src = p.tiles + ((int64_t)(r0 + prow) * p.kt + pk) * (int64_t)F::TILE;
+        mbar_expect_tx(bars_s + 8 * pd, nt * F::TILE);
+        bulk_load(ring_s + pd * slot_bytes, src, nt * F::TILE, bars_s + 8 * pd);
+        if (++pd == p.depth) pd = 0;
+        pk += nt;
+        producer_skip_empty();
+    };
+    B200Q_TRACE_POINT(6);
     if (lane == 0)
-        while (issued < total && issued < p.depth) issue_next();
+        for (int d = 0; d < p.depth && prow < nrows; d++) issue_next();
+    B200Q_TRACE_POINT(7);
 
+    // Lane constants for the staged activations (see XCols).
+    int lane_chunk, swz_a, swz_b;
+    if constexpr (TYPE == kQ6_K) {
+        lane_chunk = 16 * (t >> 1) + 2 * (t & 1), swz_a = 0, swz_b = (t >> 1) * 64;
+    } else {
+        lane_chunk = 8 * t, swz_a = (t & 1) * 32, swz_b = (t >> 1) * 64;
+    }
     XBase<NB> xb;
 #pragma unroll
     for (int nb = 0; nb < NB; nb++) {
         const int col = min(g + 8 * nb, p.m - 1);
-        // the lane's K-quarter t starts TK/4 values = TK/32 chunks into each tile
-        xb.x[nb] = smem_u32(xs + col * xs_stride) + t * (F::TK / 32) * 16;
+        xb.x[nb] = smem_u32(xs + col * xs_stride) + lane_chunk * 16;
         if constexpr (F::SUB != 0) {
-            // the lane's sub-blocks start (TK/4)/SUB entries into each tile's aux range
-            xb.shi[nb] = smem_u32(shi + col * ns) + t * (F::TK / 4 / F::SUB) * 2;
-            xb.slo[nb] = smem_u32(slo + col * ns) + t * (F::TK / 4 / F::SUB) * 2;
+            xb.shi[nb] = smem_u32(shi + col * ns) + t * F::AUX_PER_LANE * 2;
+            xb.slo[nb] = smem_u32(slo + col * ns) + t * F::AUX_PER_LANE * 2;
         } else {
             xb.shi[nb] = xb.slo[nb] = 0;
         }
     }
 
+    if (kt_begin < kt_end) stage_x<TYPE>(p, (int64_t)kt_begin * F::TK, (kt_end - kt_begin) * F::TK, xs_stride, ns, xs, shi, slo);
+    __syncthreads();
+    B200Q_TRACE_POINT(1);
+
     int cd = 0;
     uint32_t cphase = 0;
     bool timed_out = false;
-    for (int64_t kt0 = kt_begin; kt0 < kt_end; kt0 += p.ktc) {
-        const int nkt = (int)min((int64_t)p.ktc, kt_end - kt0);
-        if (kt0 != kt_begin) __syncthreads();  // everyone is done reading the previous chunk
-        stage_x<TYPE>(p, kt0 * F::TK, nkt * F::TK, xs_stride, ns, xs, shi, slo);
-        __syncthreads();
-        for (int j = 0; j < nj; j++) {
-            float acc[2][NB][4];
+    int crow = 0, cpart = warp;
+    while (cpart >= p.kp) cpart -= p.kp, crow++;
+    for (; crow < nrows && nunits != 0;) {
+        float acc[2][NB][4];
 #pragma unroll
-            for (int a = 0; a < 2; a++)
-#pragma unroll
-                for (int nb = 0; nb < NB; nb++)
-#pragma unroll
-                    for (int i = 0; i < 4; i++) acc[a][nb][i] = 0.0f;
-            for (int kl = 0; kl < nkt; kl++) {
-                if (!mbar_wait(bars_s + 8 * cd, cphase)) timed_out = true;
-                const uint32_t slot = ring_s + cd * F::TILE + lane * 16;
-                XCols<NB> xc;
-                xcols_for_tile<NB>(xc, xb, kl * (F::TK / 8), F::SUB ? kl * (F::TK / F::SUB) : 0, t);
-                if constexpr (TYPE == kQ4_0) {
-                    tile_q4_0<NB>(slot, xc, acc);
-                } else if constexpr (TYPE == kQ8_0) {
-                    tile_q8_0<NB>(slot, xc, acc);
-                } else if constexpr (TYPE == kQ4_K) {
-                    tile_q4_k<NB>(slot, xc, acc);
-                } else {
-                    tile_q6_k<NB>(slot, ring_s + cd * F::TILE + F::LOADS * 512 + lane * 4, xc, acc);
-                }
-                if (++cd == p.depth) cd = 0, cphase ^= 1;
-                __syncwarp();  // all lanes have read the slot
-                if (lane == 0 && issued < total) {
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    issue_next();
-                }
-            }
-            // Park the partial sums of this row tile; later chunks of the same K slice add to them.
-            float *r = red + (size_t)(j * nwarps + warp) * NB * 128 + lane;
+        for (int a = 0; a < 2; a++)
 #pragma unroll
             for (int nb = 0; nb < NB; nb++)
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    float *q = r + (nb * 4 + i) * 32;
-                    const float v = acc[0][nb][i] + acc[1][nb][i];
-                    *q = (kt0 == kt_begin) ? v : *q + v;
+                for (int i = 0; i < 4; i++) acc[a][nb][i] = 0.0f;
+        const int k0 = kt_begin + cpart * p.ktp, k1 = min(k0 + p.ktp, kt_end);
+        for (int kt = k0; kt < k1;) {
+            const int nt = min(p.tps, k1 - kt);
+            if (!mbar_wait(bars_s + 8 * cd, cphase)) timed_out = true;
+#ifdef B200Q_TRACE
+            if (crow == 0 && kt == k0) B200Q_TRACE_POINT(2);
+#endif
+            for (int ti = 0; ti < nt; ti++) {
+                const uint32_t tile = ring_s + cd * slot_bytes + ti * F::TILE;
+                const int kl = kt + ti - kt_begin;  // tile index inside the staged slice
+                XCols<NB> xc;
+                xcols_for_tile<NB>(xc, xb, kl * 32, F::SUB ? kl * (F::TK / F::SUB) : 0, swz_a, swz_b);
+                if constexpr (TYPE == kQ4_0) {
+                    tile_q4_0<NB>(tile, lane, xc, nc, acc);
+                } else if constexpr (TYPE == kQ8_0) {
+                    tile_q8_0<NB>(tile, lane, xc, acc);
+                } else if constexpr (TYPE == kQ4_K) {
+                    tile_q4_k<NB>(tile, lane, xc, nc, acc);
+                } else {
+                    tile_q6_k<NB>(tile, lane, xc, acc);
                 }
+            }
+            kt += nt;
+            if (++cd == p.depth) cd = 0, cphase ^= 1;
+            __syncwarp();  // all lanes have read the slot
+            if (lane == 0 && prow < nrows) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                issue_next();
+            }
         }
+        float *r = red + (size_t)(crow * p.kp + cpart) * NB * 128 + lane;
+#pragma unroll
+        for (int nb = 0; nb < NB; nb++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) r[(nb * 4 + i) * 32] = acc[0][nb][i] + acc[1][nb][i];
+        cpart += nwarps;
+        while (cpart >= p.kp) cpart -= p.kp, crow++;
     }
     if (timed_out && lane == 0) atomicExch(p.status, 2);
+    B200Q_TRACE_POINT(3);
 
     cg::cluster_group cluster = cg::this_cluster();
     if (p.splits > 1) cluster.sync(); else __syncthreads();
+    B200Q_TRACE_POINT(4);
 
-    // Element e of `red`: lane = e & 31, i = (e >> 5) & 3, nb, warp, j.  D fragment element i of lane
-    // (g, t): row g + 8*(i>>1) of the row tile, batch column 2t + (i&1) + 8*nb.
-    const int maxnj_cl = (int)((r1 - r0 + nwarps - 1) / nwarps);
-    const int total_e = maxnj_cl * nwarps * NB * 128;
+    // Output element e: lane = e & 31, i = (e >> 5) & 3, nb, row tile.  D fragment element i of lane
+    // (g, t): row g + 8*(i>>1) of the row tile, batch column 2t + (i&1) + 8*nb.  Each value is the
+    // sum over the k parts of every split, added in a fixed order.
+    const int total_e = nrows * NB * 128;
     const int per = (total_e + p.splits - 1) / p.splits;
     const int e_end = min((split + 1) * per, total_e);
     for (int e = split * per + (int)threadIdx.x; e < e_end; e += blockDim.x) {
-        const int ln = e & 31, i = (e >> 5) & 3, nb = (e >> 7) % NB, wj = (e >> 7) / NB;
-        const int wq = wj % nwarps, j = wj / nwarps;
-        const int64_t rtile = r0 + wq + (int64_t)j * nwarps;
-        const int64_t row = rtile * 16 + (ln >> 2) + 8 * (i >> 1);
+        const int ln = e & 31, i = (e >> 5) & 3, nb = (e >> 7) % NB, ri = (e >> 7) / NB;
+        const int64_t row = (int64_t)(r0 + ri) * 16 + (ln >> 2) + 8 * (i >> 1);
         const int col = 8 * nb + 2 * (ln & 3) + (i & 1);
-        if (rtile < r1 && row < p.n && col < p.m) {
+        if (row < p.n && col < p.m) {
             float v = 0.0f;
-            if (p.splits > 1) {
-                for (int r = 0; r < p.splits; r++) {
-                    // a split whose K slice is empty parked nothing
-                    if ((int64_t)r * p.kts < p.kt) v += *cluster.map_shared_rank(red + e, r);
+            const int within = (e & 127) + nb * 128;  // offset inside a unit's block
+            for (int r = 0; r < p.splits; r++) {
+                if ((int64_t)r * p.kts >= p.kt) break;  // that split has no K slice and parked nothing
+                const float *base = p.splits > 1 ? cluster.map_shared_rank(red, r) : red;
+                for (int q = 0; q < p.kp; q++) {
+                    // a part that lies beyond the split's slice parked nothing
+                    if ((int64_t)r * p.kts + (int64_t)q * p.ktp >= min((int64_t)(r + 1) * p.kts, p.kt)) break;
+                    v += base[(size_t)(ri * p.kp + q) * NB * 128 + within];
                 }
-            } else {
-                v = red[e];
             }
             if (p.bias != nullptr) v += __ldg(p.bias + row);
             p.y[(int64_t)col * p.y_ld + row] = apply_activation(p.act, v);
         }
     }
     if (p.splits > 1) cluster.sync();  // keep shared memory alive until every peer has read it
+    B200Q_TRACE_POINT(5);
 }
+
+#ifdef B200Q_TRACE
+}  // namespace
+}  // namespace b200q
+extern "C" int b200q_debug_set_trace(unsigned long long *dev_buf) {
+    return cudaMemcpyToSymbol(b200q::g_trace, &dev_buf, sizeof(dev_buf)) == cudaSuccess ? 0 : -3;
+}
+namespace b200q {
+namespace {
+#endif
 
 int env_int(const char *name, int dflt) {
     const char *v = std::getenv(name);
@@ -688,6 +779,42 @@ int env_int(const char *name, int dflt) {
 constexpr size_t kSmemLimit = 227 * 1024;
 constexpr int kMaxWarps = 16;
 
+struct Plan {
+    int splits, nclusters, warps, kp;
+    double cost;
+};
+
+// Picks cluster splits S, k parts per row tile KP and warps W.  Cost model: the busiest warp of the
+// busiest CTA sets the time, so minimise its tile count; small penalties for cluster size (barriers,
+// partial-sum traffic) and for leaving SMs idle.
+Plan make_plan(int64_t rt, int64_t kt, int sms, size_t x_bytes_per_ktile, size_t x_limit, size_t unit_red_bytes) {
+    Plan best{1, 1, 1, 1, 1e30};
+    for (int s = 1; s <= 8; s *= 2) {
+        if (s > kt) break;
+        const int64_t kts = (kt + s - 1) / s;
+        if ((size_t)kts * x_bytes_per_ktile > x_limit && s < 8 && s * 2 <= kt) continue;
+        const int ncl = (int)std::max<int64_t>(1, std::min<int64_t>(sms / s, rt));
+        const int64_t rc = (rt + ncl - 1) / ncl;
+        for (int kp = 1; kp <= kts && kp <= 16; kp++) {
+            const int64_t ktp = (kts + kp - 1) / kp;
+            if (ktp < 2 && kp > 1) break;  // keep at least two tiles per unit
+            const int64_t units = rc * kp;
+            // staged x plus the per-unit partial sums must leave room for the tile rings
+            if ((size_t)kts * x_bytes_per_ktile + (size_t)units * unit_red_bytes > 150 * 1024 && kp > 1) break;
+            for (int w = 1; w <= kMaxWarps; w++) {
+                const int64_t rounds = (units + w - 1) / w;
+                double cost = (double)(rounds * ktp);
+                cost *= 1.0 + 0.03 * (s > 1 ? std::log2((double)s) : 0.0);
+                cost *= 1.0 + 0.01 * (kp - 1);                       // more partial sums to add
+                cost *= 1.0 + 0.25 * (kMaxWarps - w) / kMaxWarps;    // fewer warps hide less latency
+                cost *= (double)sms / (double)(ncl * s);             // idle SMs
+                if (cost < best.cost) best = Plan{s, ncl, w, kp, cost};
+            }
+        }
+    }
+    return best;
+}
+
 template <int TYPE, int NB>
 int launch_t(const Weight &w, const GemvParams &p0, cudaStream_t s) {
     using F = Fmt<TYPE>;
@@ -695,62 +822,42 @@ int launch_t(const Weight &w, const GemvParams &p0, cudaStream_t s) {
     int dev_sms = 148;
     cudaDeviceGetAttribute(&dev_sms, cudaDevAttrMultiProcessorCount, w.device);
 
-    // K splits (CTAs per cluster).  Two halves of K per row group measured best for every decoder
-    // shape on B200; matrices with few rows (N <= 16 * #SMs) need four to give all SMs work.
-    int splits = w.kt >= 2 ? 2 : 1;
-    if (w.rt <= dev_sms && w.kt >= 4) splits = 4;
-    if (w.kt % splits != 0)  // prefer an even split when one exists nearby
-        for (int sp = splits; sp <= 8 && sp <= w.kt; sp++)
-            if (w.kt % sp == 0) { splits = sp; break; }
-    splits = std::max(1, std::min(8, env_int("B200Q_GEMV_SPLITS", splits)));
-    splits = (int)std::min<int64_t>(splits, w.kt);
-    p.splits = splits;
-    p.kts = (int)((w.kt + splits - 1) / splits);
+    const size_t x_per_ktile = (size_t)p.m * (F::TK * 2 + (F::SUB ? 4 * (F::TK / F::SUB) : 0));
+    Plan plan = make_plan(w.rt, w.kt, dev_sms, x_per_ktile, (size_t)env_int("B200Q_GEMV_XSMEM", 96 * 1024),
+                          (size_t)NB * 128 * sizeof(float));
+    plan.splits = std::max(1, std::min<int>({8, (int)w.kt, env_int("B200Q_GEMV_SPLITS", plan.splits)}));
+    if (std::getenv("B200Q_GEMV_SPLITS")) plan.nclusters = (int)std::max<int64_t>(1, std::min<int64_t>(dev_sms / plan.splits, w.rt));
+    plan.nclusters = (int)std::max<int64_t>(1, std::min<int64_t>(env_int("B200Q_GEMV_CLUSTERS", plan.nclusters), w.rt));
+    p.splits = 1;
+    p.split_shift = 0;
+    while (p.splits * 2 <= plan.splits) p.splits *= 2, p.split_shift++;  // power of two
+    p.kts = (int)((w.kt + p.splits - 1) / p.splits);
+    p.nclusters = plan.nclusters;
+    p.rows_q = (int)(w.rt / p.nclusters), p.rows_r = (int)(w.rt % p.nclusters);
+    p.kp = std::max(1, std::min(p.kts, env_int("B200Q_GEMV_KP", plan.kp)));
+    p.ktp = (p.kts + p.kp - 1) / p.kp;
+    int warps = std::max(1, std::min(kMaxWarps, env_int("B200Q_GEMV_WARPS", plan.warps)));
+    const int64_t rows_per_cluster = (w.rt + p.nclusters - 1) / p.nclusters;
+    p.maxunits = (int)(rows_per_cluster * p.kp);
+    p.tps = std::max(1, std::min(p.ktp, env_int("B200Q_GEMV_TPS", F::TILE <= 2304 ? 2 : 1)));
 
-    // One cluster per `splits` SMs, but never more clusters than row tiles.
-    int nclusters = std::max(1, dev_sms / splits);
-    nclusters = env_int("B200Q_GEMV_CLUSTERS", nclusters);
-    nclusters = (int)std::max<int64_t>(1, std::min<int64_t>(nclusters, w.rt));
-    p.nclusters = nclusters;
-    const int64_t rows_per_cluster = (w.rt + nclusters - 1) / nclusters;
-
-    // Staged x chunk: as much of the K slice as fits the x budget.
-    const size_t per_tile_x = (size_t)p.m * (F::TK * 2 + (F::SUB ? 4 * (F::TK / F::SUB) : 0));
-    const size_t x_budget = (size_t)env_int("B200Q_GEMV_XSMEM", 48 * 1024);
-    const int ktc = (int)std::max<size_t>(1, std::min<size_t>((x_budget - p.m * 16) / per_tile_x, p.kts));
-    p.ktc = ktc;
     const size_t x_bytes =
-        (((size_t)p.m * (ktc * F::TK + 8) * 2 + (F::SUB ? (size_t)p.m * (ktc * F::TK / F::SUB) * 4 : 0)) + 15) & ~(size_t)15;
-
-    // Warps per CTA: each warp walks whole row tiles, so prefer the count that needs the fewest
-    // rounds and wastes the fewest warp-slots in the last round; then shrink until the per-warp
-    // tile rings (at least two slots each, if possible) fit in shared memory next to x.
-    int warps = 1;
-    {
-        int64_t best = INT64_MAX;
-        for (int wc = 1; wc <= kMaxWarps; wc++) {
-            const int64_t rounds = (rows_per_cluster + wc - 1) / wc;
-            const int64_t cost = rounds * 64 + (rounds * wc - rows_per_cluster);  // time first, waste second
-            if (cost <= best) best = cost, warps = wc;
-        }
-    }
-    warps = std::max(1, std::min(kMaxWarps, env_int("B200Q_GEMV_WARPS", warps)));
-    size_t fixed = 0, bar_bytes = 0;
+        (((size_t)p.m * (p.kts * F::TK + 8) * 2 + (F::SUB ? (size_t)p.m * (p.kts * F::TK / F::SUB) * 4 : 0)) + 15) & ~(size_t)15;
+    const size_t red_bytes = (size_t)p.maxunits * NB * 128 * sizeof(float);
+    const size_t fixed = (x_bytes + red_bytes + 127) & ~(size_t)127;
+    const size_t slot_bytes = (size_t)p.tps * F::TILE;
     int depth = 0;
-    for (;; warps--) {
-        p.maxnj = (int)((rows_per_cluster + warps - 1) / warps);
-        const size_t red_bytes = (size_t)p.maxnj * warps * NB * 128 * sizeof(float);
-        fixed = (x_bytes + red_bytes + 127) & ~(size_t)127;
-        bar_bytes = (size_t)warps * 8 * 8;  // depth <= 8
-        depth = fixed + bar_bytes < kSmemLimit ? (int)((kSmemLimit - fixed - bar_bytes) / ((size_t)warps * F::TILE)) : 0;
+    for (;; warps--) {  // shrink the CTA until every warp gets at least two ring slots
+        const size_t bar_bytes = (size_t)warps * 8 * 8;
+        depth = fixed + bar_bytes < kSmemLimit ? (int)((kSmemLimit - fixed - bar_bytes) / ((size_t)warps * slot_bytes)) : 0;
         if (depth >= 2 || warps == 1) break;
     }
-    if (depth < 1) return fail(B200Q_EINVAL, "gemv: shared memory budget exceeded for this shape");
-    const int64_t tiles_per_warp = (int64_t)p.maxnj * p.kts;
-    depth = (int)std::max<int64_t>(1, std::min<int64_t>({(int64_t)depth, (int64_t)8, tiles_per_warp}));
+    if (depth < 1) return fail(B200Q_EINVAL, "gemv: K is too large for the shared-memory staging of this batch size");
+    const int64_t slots_per_warp = ((p.maxunits + warps - 1) / warps) * ((p.ktp + p.tps - 1) / p.tps);
+    depth = (int)std::max<int64_t>(1, std::min<int64_t>({(int64_t)depth, (int64_t)8, slots_per_warp}));
     depth = std::max(1, std::min(depth, env_int("B200Q_GEMV_DEPTH", depth)));
     p.depth = depth;
-    const size_t smem = fixed + (size_t)warps * depth * F::TILE + (size_t)warps * depth * 8;
+    const size_t smem = fixed + (size_t)warps * depth * slot_bytes + (size_t)warps * depth * 8;
 
     auto kern = gemv_mma_kernel<TYPE, NB>;
     static thread_local bool configured[16] = {};
@@ -759,13 +866,13 @@ int launch_t(const Weight &w, const GemvParams &p0, cudaStream_t s) {
         configured[w.device & 15] = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(nclusters * splits), 1, 1);
+    cfg.gridDim = dim3((unsigned)(p.nclusters * p.splits), 1, 1);
     cfg.blockDim = dim3(warps * 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = splits;
+    attr[0].val.clusterDim.x = p.splits;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;

@@ -183,12 +183,15 @@ def test_70b_shapes_sampled_rows_and_sharding(oracle, n, k):
     assert rel_err(y[:, rows].cpu().numpy(), ref) <= TOL_GEMV
     # linearity in x (up to the fp16 staging of activations)
     y2 = g.quantized_dense(xd * 2.0, wr, quant(t))
-    assert torch.equal(y2, y * 2.0)  # scaling by a power of two is exact in every rounding step
-    # a row shard computes exactly the corresponding slice of the full result
+    # exact up to activations that land in the fp16 subnormal range when they are staged
+    assert float((y2 - y * 2.0).abs().max()) <= 1e-4 * float(y.abs().max())
+    # a row shard computes the corresponding slice of the full result (the split of K over CTAs, and
+    # with it the order of the f32 partial sums, may differ between the two launches)
     for rank in (0, 5):
         ws = g.upload(w, t, shard=(rank, 8))
         ys = g.quantized_dense(xd, ws, quant(t))
-        assert torch.equal(ys, y[:, ws.row_begin:ws.row_begin + ws.n])
+        ref_slice = y[:, ws.row_begin:ws.row_begin + ws.n]
+        assert float((ys - ref_slice).abs().max()) <= 1e-5 * float(y.abs().max())
         ws.free()
     wr.free()
 
