@@ -1,7 +1,479 @@
-// Prefill GEMM (m > 16): placeholder until the tcgen05 kernel lands.
+// Prefill GEMM (m > 16) for GGML block-quantized weights on sm_100a: tcgen05 MMA with TMEM
+// accumulators, the packed weights dequantized on the fly into the MMA's shared-memory operand.
+//
+// Computes compute.Function.FusedQuantizedDense (core/graph/fused_ops.go:195-245 in gomlx/gomlx):
+//     y[m, n] = act(sum_k x[m, k] * dequant(W)[n, k] + bias[n])
+//
+// One CTA computes a 128 (batch rows) x 128 (weight rows) tile of y over all of K.
+//   warp 0      producer: TMA tensor loads of the bf16 activation tile (128 x 64, 128-byte swizzle)
+//               and TMA bulk copies of the packed weight tiles (8 row tiles x 256 values per stage)
+//   warp 1      allocates TMEM and issues tcgen05.mma (one elected lane): D[128 x 128] f32 in TMEM,
+//               A = activations, B = dequantized weights, both K-major bf16 in shared memory
+//   warps 2-9   dequantize: thread (weight row, half) turns 32 packed values per 64-wide k stage into
+//               bf16 and writes them in the UMMA 128-byte-swizzled K-major layout; afterwards the same
+//               warps read the accumulator back with tcgen05.ld and apply bias / activation
+// All hand-offs go through mbarriers; every wait is bounded and records a timeout in the weight's
+// status word instead of spinning forever.
+//
+// Dequantization evaluates the reference formula in f32 (ml/ggml/dequant.go:56-115 for Q8_0 / Q4_0)
+// and rounds once to bf16, so the only deviation from the f32 reference is the bf16 rounding of the
+// two MMA operands; accumulation is f32.  f32 activations are converted to bf16 by a small kernel into
+// a stream-ordered scratch buffer first.
 #include "common.cuh"
+
+#include <cuda.h>
+
+#include <mutex>
+
 namespace b200q {
-int launch_gemm(const Weight &, const void *, int, int64_t, const float *, int, float *, int64_t, cudaStream_t) {
-    return fail(B200Q_ENOTIMPL, "dense: m > 16 is not implemented yet");
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64;
+constexpr int SA = 4;                    // activation stages (16 KB each)
+constexpr int SB = 4;                    // dequantized weight stages (16 KB each)
+constexpr int SP = 2;                    // packed weight stages (8 tiles each)
+constexpr int kDequantWarps = 8;
+constexpr int kThreads = 32 * (2 + kDequantWarps);
+constexpr int kGemmSpinLimit = 1 << 24;
+
+struct GemmParams {
+    const uint8_t *tiles;
+    const float *bias;
+    float *y;
+    int *status;
+    int64_t m, n, y_ld;
+    int64_t rt, kt;
+    int act;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait; on expiry records a timeout and returns false.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *status) {
+    for (int spin = 0; spin < kGemmSpinLimit; spin++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    atomicExch(status, 2);
+    return false;
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;                  // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset
+    d |= (uint64_t)1 << 46;                  // descriptor version
+    d |= (uint64_t)2 << 61;                  // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: D f32, A and B bf16, both K-major, M = 128, N = 128.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+__device__ __forceinline__ float h16(uint32_t bits) { return __half2float(__ushort_as_half((unsigned short)bits)); }
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds8(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, const uint4 &v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+
+// ---------------------------------------------------------------------------------------
+// Dequantization of 32 consecutive values (group kq = 0..7 of a 256-value tile) of tile row r
+// into bf16, natural order: out[c] holds values 8c .. 8c+7.  Integer codes are turned into
+// floats exactly (fp16 exponent-magic, then widened); the scale is applied by one f32 FMA whose
+// exact argument equals the reference formula, so the f32 value is the reference's and only the
+// final rounding to bf16 differs.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float2 h2_to_f2(uint32_t h2) {
+    return __half22float2(*reinterpret_cast<const __half2 *>(&h2));
+}
+// Four codes given as fp16 pairs (v0, v2), (v1, v3) [nibble words] -> two packed bf16x2 in natural order.
+__device__ __forceinline__ void emit4_02_13(uint32_t p02, uint32_t p13, float s, float o, uint32_t &w01, uint32_t &w23) {
+    const float2 a = h2_to_f2(p02), b = h2_to_f2(p13);
+    w01 = pack_bf16(fmaf(a.x, s, o), fmaf(b.x, s, o));
+    w23 = pack_bf16(fmaf(a.y, s, o), fmaf(b.y, s, o));
+}
+// Four codes given as fp16 pairs (v0, v1), (v2, v3) [byte words].
+__device__ __forceinline__ void emit4_01_23(uint32_t p01, uint32_t p23, float s, float o, uint32_t &w01, uint32_t &w23) {
+    const float2 a = h2_to_f2(p01), b = h2_to_f2(p23);
+    w01 = pack_bf16(fmaf(a.x, s, o), fmaf(a.y, s, o));
+    w23 = pack_bf16(fmaf(b.x, s, o), fmaf(b.y, s, o));
+}
+// Eight nibbles of a word pair (low or high nibbles of 8 consecutive bytes) -> one 16-byte chunk.
+template <bool HIGH>
+__device__ __forceinline__ uint4 nibble_chunk(uint32_t w0, uint32_t w1, float s, float o) {
+    constexpr uint32_t MASK = HIGH ? 0x00F000F0u : 0x000F000Fu, MAGIC = HIGH ? 0x54005400u : 0x64006400u;
+    uint4 c;
+    emit4_02_13((w0 & MASK) | MAGIC, ((w0 >> 8) & MASK) | MAGIC, s, o, c.x, c.y);
+    emit4_02_13((w1 & MASK) | MAGIC, ((w1 >> 8) & MASK) | MAGIC, s, o, c.z, c.w);
+    return c;
+}
+// Eight bytes holding unsigned codes -> one chunk (codes read as 1024 + code).
+__device__ __forceinline__ uint4 byte_chunk(uint32_t w0, uint32_t w1, float s, float o) {
+    uint4 c;
+    emit4_01_23(__byte_perm(w0, 0x64646464u, 0x5140), __byte_perm(w0, 0x64646464u, 0x7362), s, o, c.x, c.y);
+    emit4_01_23(__byte_perm(w1, 0x64646464u, 0x5140), __byte_perm(w1, 0x64646464u, 0x7362), s, o, c.z, c.w);
+    return c;
+}
+
+template <int TYPE>
+__device__ __forceinline__ void dequant32(uint32_t tile, int r, int kq, uint4 (&out)[4]) {
+    const int g = r & 7, rs = r >> 3;
+    if constexpr (TYPE == kQ4_0) {  // (q - 8) * d, dequant.go:83-115
+        const int t = kq >> 1, bp = kq & 1;
+        const float d = h16(lds16(tile + r * 16 + kq * 2));
+        const uint4 q = lds128(tile + 256 + (2 * bp + rs) * 512 + (4 * g + t) * 16);
+        out[0] = nibble_chunk<false>(q.x, q.y, d, -1032.0f * d);
+        out[1] = nibble_chunk<false>(q.z, q.w, d, -1032.0f * d);
+        out[2] = nibble_chunk<true>(q.x, q.y, d, -72.0f * d);
+        out[3] = nibble_chunk<true>(q.z, q.w, d, -72.0f * d);
+    } else if constexpr (TYPE == kQ8_0) {  // q * d, dequant.go:58-78
+        const int t = kq >> 1, bp = kq & 1;
+        const float d = h16(lds16(tile + r * 16 + kq * 2));
+        const uint4 a = lds128(tile + 256 + (2 * (2 * bp) + rs) * 512 + (4 * g + t) * 16);
+        const uint4 b = lds128(tile + 256 + (2 * (2 * bp + 1) + rs) * 512 + (4 * g + t) * 16);
+        const float o = -1152.0f * d;  // codes are read as 1024 + (q + 128)
+        out[0] = byte_chunk(a.x ^ 0x80808080u, a.y ^ 0x80808080u, d, o);
+        out[1] = byte_chunk(a.z ^ 0x80808080u, a.w ^ 0x80808080u, d, o);
+        out[2] = byte_chunk(b.x ^ 0x80808080u, b.y ^ 0x80808080u, d, o);
+        out[3] = byte_chunk(b.z ^ 0x80808080u, b.w ^ 0x80808080u, d, o);
+    } else if constexpr (TYPE == kQ4_K) {  // (d*sc)*q - dmin*m
+        const int G = kq >> 1, hi = kq & 1;
+        const uint4 h = lds128(tile + r * 16);
+        const float d = h16(h.x & 0xFFFFu), dmin = h16(h.x >> 16);
+        const uint32_t s03 = h.y, s47 = h.z, s8b = h.w;  // scales[0..3], [4..7], [8..11]
+        uint32_t sc, mn;
+        if (kq < 4) {
+            sc = (s03 >> (8 * kq)) & 63u;
+            mn = (s47 >> (8 * kq)) & 63u;
+        } else {
+            const int j = kq - 4;
+            sc = ((s8b >> (8 * j)) & 0x0Fu) | (((s03 >> (8 * j + 6)) & 3u) << 4);
+            mn = ((s8b >> (8 * j + 4)) & 0x0Fu) | (((s47 >> (8 * j + 6)) & 3u) << 4);
+        }
+        const float ds = d * (float)sc, dm = dmin * (float)mn;
+        const uint4 q0 = lds128(tile + 256 + rs * 512 + (4 * g + G) * 16);
+        const uint4 q1 = lds128(tile + 256 + (2 + rs) * 512 + (4 * g + G) * 16);
+        if (hi) {
+            const float o = fmaf(-64.0f, ds, -dm);
+            out[0] = nibble_chunk<true>(q0.x, q0.y, ds, o);
+            out[1] = nibble_chunk<true>(q0.z, q0.w, ds, o);
+            out[2] = nibble_chunk<true>(q1.x, q1.y, ds, o);
+            out[3] = nibble_chunk<true>(q1.z, q1.w, ds, o);
+        } else {
+            const float o = fmaf(-1024.0f, ds, -dm);
+            out[0] = nibble_chunk<false>(q0.x, q0.y, ds, o);
+            out[1] = nibble_chunk<false>(q0.z, q0.w, ds, o);
+            out[2] = nibble_chunk<false>(q1.x, q1.y, ds, o);
+            out[3] = nibble_chunk<false>(q1.z, q1.w, ds, o);
+        }
+    } else {  // Q6_K: (d*sc)*(q - 32); values 32kq .. 32kq+31 = 128n + 32c + l
+        const int n = kq >> 2, c = kq & 3, part = c & 1;
+        const float d = h16(lds16(tile + 3328 + r * 2));
+#pragma unroll
+        for (int lh = 0; lh < 2; lh++) {
+            const int lane = 4 * g + 2 * n + lh;
+            const uint4 ql = lds128(tile + 256 + (2 * part + rs) * 512 + lane * 16);
+            const uint4 qh = lds128(tile + 256 + (4 + rs) * 512 + lane * 16);
+            const int sc = (int)(int8_t)lds8(tile + r * 16 + 8 * n + 2 * c + lh);
+            const float ds = d * (float)sc, o = -1056.0f * ds;  // codes are read as 1024 + q
+            const uint32_t lw[4] = {ql.x, ql.y, ql.z, ql.w}, hw[4] = {qh.x, qh.y, qh.z, qh.w};
+            uint32_t code[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t nib = (c < 2 ? lw[i] : (lw[i] >> 4)) & 0x0F0F0F0Fu;
+                code[i] = nib | (((hw[i] >> (2 * c)) & 0x03030303u) << 4);
+            }
+            out[2 * lh] = byte_chunk(code[0], code[1], ds, o);
+            out[2 * lh + 1] = byte_chunk(code[2], code[3], ds, o);
+        }
+    }
+}
+
+template <int TYPE>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
+    using F = Fmt<TYPE>;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // carve: A stages | B stages | packed stages | barriers | tmem slot   (A/B need 1024-byte alignment)
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, P_BYTES = 8 * F::TILE;
+    const uint32_t a_s = smem_u32(smem), b_s = a_s + SA * A_BYTES, p_s = b_s + SB * B_BYTES;
+    const uint32_t bar_s = p_s + SP * P_BYTES;
+    // barrier indices
+    const uint32_t a_full = bar_s, a_empty = a_full + 8 * SA, b_full = a_empty + 8 * SA, b_empty = b_full + 8 * SB;
+    const uint32_t p_full = b_empty + 8 * SB, p_empty = p_full + 8 * SP, d_full = p_empty + 8 * SP;
+    const uint32_t tmem_slot = d_full + 8;
+    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(smem + (tmem_slot - a_s));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t m0 = (int64_t)blockIdx.y * BM;
+    const int64_t rt0 = (int64_t)blockIdx.x * (BN / 16);
+    const int nrt = (int)min((int64_t)(BN / 16), p.rt - rt0);  // row tiles that exist in this column tile
+    const int64_t nstages = p.kt * 4;                            // 64-wide k stages
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < SA; i++) mbar_init(a_full + 8 * i, 1), mbar_init(a_empty + 8 * i, 1);
+        for (int i = 0; i < SB; i++) mbar_init(b_full + 8 * i, kDequantWarps), mbar_init(b_empty + 8 * i, 1);
+        for (int i = 0; i < SP; i++) mbar_init(p_full + 8 * i, 1), mbar_init(p_empty + 8 * i, kDequantWarps);
+        mbar_init(d_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {  // TMEM: 128 columns of f32 accumulators
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // producer: packed weights every 4th stage, activations every stage
+            for (int64_t ks = 0; ks < nstages; ks++) {
+                if ((ks & 3) == 0) {
+                    const int64_t kt = ks >> 2;
+                    const int sp = (int)(kt % SP);
+                    if (!mbar_wait(p_empty + 8 * sp, (uint32_t)(((kt / SP) & 1) ^ 1), p.status)) break;
+                    mbar_expect_tx(p_full + 8 * sp, nrt * F::TILE);
+                    for (int i = 0; i < nrt; i++)
+                        bulk_load(p_s + sp * P_BYTES + i * F::TILE, p.tiles + ((rt0 + i) * p.kt + kt) * (int64_t)F::TILE,
+                                  F::TILE, p_full + 8 * sp);
+                }
+                const int sa = (int)(ks % SA);
+                if (!mbar_wait(a_empty + 8 * sa, (uint32_t)(((ks / SA) & 1) ^ 1), p.status)) break;
+                mbar_expect_tx(a_full + 8 * sa, A_BYTES);
+                tma_load_2d(a_s + sa * A_BYTES, &xmap, (int)(ks * BK), (int)m0, a_full + 8 * sa);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            for (int64_t ks = 0; ks < nstages; ks++) {
+                const int sa = (int)(ks % SA), sb = (int)(ks % SB);
+                if (!mbar_wait(a_full + 8 * sa, (uint32_t)((ks / SA) & 1), p.status)) break;
+                if (!mbar_wait(b_full + 8 * sb, (uint32_t)((ks / SB) & 1), p.status)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t ad = umma_desc(a_s + sa * A_BYTES), bd = umma_desc(b_s + sb * B_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / 16; k++)  // +32 bytes along K inside the 128-byte swizzle atom
+                    umma_bf16(tmem_d, ad + 2 * k, bd + 2 * k, (ks > 0 || k > 0) ? 1u : 0u);
+                umma_commit(a_empty + 8 * sa);
+                umma_commit(b_empty + 8 * sb);
+            }
+            umma_commit(d_full);
+        }
+    } else {
+        // dequantize: thread = (weight row n of the tile, half of the 64-wide stage)
+        const int dt = threadIdx.x - 64, n = dt & 127, half = dt >> 7;
+        const int rtile = n >> 4, r = n & 15;
+        const bool row_exists = rtile < nrt;
+        bool ok = true;
+        for (int64_t kt = 0; kt < p.kt && ok; kt++) {
+            const int sp = (int)(kt % SP);
+            ok = mbar_wait(p_full + 8 * sp, (uint32_t)((kt / SP) & 1), p.status);
+            const uint32_t tile = p_s + sp * P_BYTES + rtile * F::TILE;
+            for (int q = 0; q < 4 && ok; q++) {
+                const int64_t ks = kt * 4 + q;
+                const int sb = (int)(ks % SB);
+                uint4 out[4];
+                if (row_exists) {
+                    dequant32<TYPE>(tile, r, 2 * q + half, out);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 4; c++) out[c] = make_uint4(0u, 0u, 0u, 0u);
+                }
+                ok = mbar_wait(b_empty + 8 * sb, (uint32_t)(((ks / SB) & 1) ^ 1), p.status);
+                const uint32_t rowbase = b_s + sb * B_BYTES + n * 128;
+#pragma unroll
+                for (int c = 0; c < 4; c++) sts128(rowbase + (((4 * half + c) ^ (n & 7)) << 4), out[c]);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(b_full + 8 * sb);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_empty + 8 * sp);
+        }
+        // epilogue: TMEM lane = batch row, column = weight row.  Warp w may read lanes 32*(w%4)..+31.
+        if (mbar_wait(d_full, 0, p.status)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int quarter = warp & 3, colhalf = (warp - 2) >> 2;
+            const int64_t row = m0 + quarter * 32 + lane;
+#pragma unroll 1
+            for (int cc = 0; cc < 2; cc++) {
+                const int col0 = colhalf * 64 + cc * 32;
+                uint32_t v[32];
+                tmem_ld32(tmem_d + ((uint32_t)(quarter * 32) << 16) + col0, v);
+                if (row < p.m) {
+                    const int64_t nbase = (int64_t)blockIdx.x * BN + col0;
+                    float *dst = p.y + row * p.y_ld + nbase;
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        if (nbase + j < p.n) {
+                            float f = __uint_as_float(v[j]);
+                            if (p.bias != nullptr) f += __ldg(p.bias + nbase + j);
+                            dst[j] = apply_activation(p.act, f);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(BN) : "memory");
+    }
+}
+
+__global__ void f32_to_bf16_kernel(const float *__restrict__ src, __nv_bfloat16 *__restrict__ dst, int64_t n) {
+    for (int64_t i = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * 4; i < n; i += (int64_t)gridDim.x * blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4 *>(src + i);
+        uint2 o;
+        o.x = pack_bf16(v.x, v.y), o.y = pack_bf16(v.z, v.w);
+        *reinterpret_cast<uint2 *>(dst + i) = o;
+    }
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = [] {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess) return (EncodeTiledFn) nullptr;
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+
+template <int TYPE>
+int launch_gemm_t(const Weight &w, const __nv_bfloat16 *x, int64_t m, const float *bias, int act, float *y, int64_t y_ld,
+                  cudaStream_t s) {
+    using F = Fmt<TYPE>;
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return fail(B200Q_ECUDA, "gemm: cuTensorMapEncodeTiled is not available");
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)w.k, (cuuint64_t)m};
+    const cuuint64_t strides[1] = {(cuuint64_t)w.k * 2};
+    const cuuint32_t box[2] = {BK, BM};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult cr = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16 *>(x), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return fail(B200Q_ECUDA, "gemm: cuTensorMapEncodeTiled failed");
+    GemmParams p{};
+    p.tiles = w.tiles, p.bias = bias, p.y = y, p.status = w.status;
+    p.m = m, p.n = w.n, p.y_ld = y_ld, p.rt = w.rt, p.kt = w.kt, p.act = act;
+    const size_t smem = 1024 + SA * BM * BK * 2 + SB * BN * BK * 2 + SP * 8 * F::TILE + 8 * (2 * SA + 2 * SB + 2 * SP + 1) + 16;
+    auto kern = gemm_tcgen05_kernel<TYPE>;
+    static thread_local bool configured[16] = {};
+    if (!configured[w.device & 15]) {
+        B200Q_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured[w.device & 15] = true;
+    }
+    dim3 grid((unsigned)((w.n + BN - 1) / BN), (unsigned)((m + BM - 1) / BM), 1);
+    kern<<<grid, kThreads, smem, s>>>(map, p);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : cuda_fail(e, "gemm launch");
+}
+
+}  // namespace
+
+int launch_gemm(const Weight &w, const void *x, int x_dtype, int64_t m, const float *bias, int act, float *y,
+                int64_t y_ld, cudaStream_t s) {
+    const __nv_bfloat16 *xb = static_cast<const __nv_bfloat16 *>(x);
+    __nv_bfloat16 *scratch = nullptr;
+    if (x_dtype == B200Q_F32) {
+        // f32 activations: convert once into a stream-ordered scratch buffer (freed after the GEMM).
+        const int64_t count = m * w.k;
+        B200Q_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&scratch), (size_t)count * 2, s));
+        const int64_t blocks = std::min<int64_t>((count / 4 + 255) / 256, 148 * 8);
+        f32_to_bf16_kernel<<<(unsigned)std::max<int64_t>(1, blocks), 256, 0, s>>>(static_cast<const float *>(x), scratch, count);
+        xb = scratch;
+    }
+    int rc;
+    switch (w.type) {
+    case kQ4_0: rc = launch_gemm_t<kQ4_0>(w, xb, m, bias, act, y, y_ld, s); break;
+    case kQ8_0: rc = launch_gemm_t<kQ8_0>(w, xb, m, bias, act, y, y_ld, s); break;
+    case kQ4_K: rc = launch_gemm_t<kQ4_K>(w, xb, m, bias, act, y, y_ld, s); break;
+    case kQ6_K: rc = launch_gemm_t<kQ6_K>(w, xb, m, bias, act, y, y_ld, s); break;
+    default: rc = fail(B200Q_ENOTIMPL, "gemm: unsupported GGML type");
+    }
+    if (scratch) cudaFreeAsync(scratch, s);
+    return rc;
+}
+
 }  // namespace b200q

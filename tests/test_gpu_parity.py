@@ -146,6 +146,45 @@ def test_batch_dims_are_restored(oracle):
     assert torch.equal(y.reshape(6, 48), g.quantized_dense(x.reshape(6, 1024), w, quant(t)))
 
 
+# ----------------------------------------------------------------------------- prefill GEMM parity (tcgen05)
+@pytest.mark.parametrize("name", list(TYPES))
+@pytest.mark.parametrize("m,n,k", [(17, 128, 256), (128, 48, 512), (200, 300, 1280), (512, 1024, 4096)])
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_gemm_parity(oracle, name, m, n, k, dtype):
+    t = TYPES[name]
+    w = oracle.make_weights(int(t), n, k, seed=11)
+    rng = np.random.default_rng(m + n)
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda()
+    bias = rng.standard_normal(n).astype(np.float32)
+    if dtype == "bf16":
+        x = x.to(torch.bfloat16)
+    # the reference upcasts bf16 activations exactly; f32 activations are rounded to bf16 by the GEMM path
+    ref = oracle.dense(int(t), w, x.float().cpu().numpy(), bias, 0, route="f64")
+    wr = g.upload(w, t)
+    y = g.quantized_dense(x, wr, quant(t), torch.from_numpy(bias).cuda())
+    assert g.last_kernel() == nat.KERNEL_GEMM_TCGEN05
+    assert nat.lib().b200q_weight_check(wr.handle, None) == 0
+    assert y.shape == (m, n)
+    assert rel_err(y.cpu().numpy(), ref) <= TOL_GEMM
+    assert torch.equal(y, g.quantized_dense(x, wr, quant(t), torch.from_numpy(bias).cuda()))
+    wr.free()
+
+
+def test_gemm_prefill_config_shapes(oracle):
+    """configs[2]: Q4_K, x bf16 [512, 4096], W 4096 x 4096 (oracle on all rows) and 4096 x 14336 (sampled rows)."""
+    t = g.GGMLQuantType.Q4_K
+    rng = np.random.default_rng(0)
+    x = torch.from_numpy(rng.standard_normal((512, 4096)).astype(np.float32)).cuda().to(torch.bfloat16)
+    xf = x.float().cpu().numpy()
+    for n in (4096, 14336):
+        w = oracle.make_weights(12, n, 4096, sigma=0.02, seed=0)
+        y = g.quantized_dense(x, w, quant(t), None, g.Activation.SILU).cpu().numpy()
+        rows = np.arange(n) if n == 4096 else np.sort(rng.choice(n, 512, replace=False))
+        pre = oracle.dense(12, np.ascontiguousarray(w[rows]), xf, route="f64")
+        ref = pre / (1.0 + np.exp(-pre))
+        assert np.abs(y[:, rows] - ref).max() <= 1.5 * TOL_GEMM * np.abs(pre).max()
+
+
 # ----------------------------------------------------------------------------- BASELINE shapes
 @pytest.mark.parametrize("name,n,k,sigma,ms", [
     ("Q8_0", 4096, 4096, 0.02, [1]),                 # configs[0]
