@@ -5,11 +5,11 @@
 //     y[m, n] = act(sum_k x[m, k] * dequant(W)[n, k] + bias[n])
 //
 // One CTA computes a 128 (batch rows) x 128 (weight rows) tile of y over all of K.
-//   warp 0      producer: TMA tensor loads of the bf16 activation tile (128 x 64, 128-byte swizzle)
-//               and TMA bulk copies of the packed weight tiles (8 row tiles x 256 values per stage)
+//   warp 0      TMA tensor loads of the bf16 activation tile (128 x 64, 128-byte swizzle)
+//   warp 2      TMA bulk copies of the packed weight tiles (8 row tiles x 256 values per stage)
 //   warp 1      allocates TMEM and issues tcgen05.mma (one elected lane): D[128 x 128] f32 in TMEM,
 //               A = activations, B = dequantized weights, both K-major bf16 in shared memory
-//   warps 2-9   dequantize: thread (weight row, half) turns 32 packed values per 64-wide k stage into
+//   warps 3-18  dequantize: thread (weight row, quarter) turns 16 packed values per 64-wide k stage into
 //               bf16 and writes them in the UMMA 128-byte-swizzled K-major layout; afterwards the same
 //               warps read the accumulator back with tcgen05.ld and apply bias / activation
 // All hand-offs go through mbarriers; every wait is bounded and records a timeout in the weight's
@@ -29,11 +29,16 @@ namespace b200q {
 namespace {
 
 constexpr int BM = 128, BN = 128, BK = 64;
-constexpr int SA = 4;                    // activation stages (16 KB each)
-constexpr int SB = 4;                    // dequantized weight stages (16 KB each)
-constexpr int SP = 2;                    // packed weight stages (8 tiles each)
-constexpr int kDequantWarps = 8;
-constexpr int kThreads = 32 * (2 + kDequantWarps);
+constexpr int kDequantWarps = 16;
+constexpr int kFirstDequantWarp = 3;     // warps 0, 1, 2: activation TMA, MMA issue, packed-weight TMA
+constexpr int kThreads = 32 * (kFirstDequantWarp + kDequantWarps);
+
+// Pipeline depths per format: activation stages (16 KB), dequantized weight stages (16 KB), packed
+// weight stages (8 tiles).  A TMA load from L2 takes about a microsecond and one stage of MMAs about
+// 0.15 us, so the activation ring has to be deep; the sizes below fill the 227 KB of shared memory.
+template <int TYPE> struct Depth { static constexpr int SA = 6, SB = 4, SP = 3; };           // Q4_0, Q4_K: 2304-byte tiles
+template <> struct Depth<kQ8_0> { static constexpr int SA = 5, SB = 3, SP = 2; };            // 4352-byte tiles
+template <> struct Depth<kQ6_K> { static constexpr int SA = 6, SB = 4, SP = 2; };            // 3360-byte tiles
 constexpr int kGemmSpinLimit = 1 << 24;
 
 struct GemmParams {
@@ -185,27 +190,28 @@ __device__ __forceinline__ uint4 byte_chunk(uint32_t w0, uint32_t w1, float s, f
     return c;
 }
 
+// 16 consecutive values: group kq = 0..7 (32 values) of the 256-value tile, half `sub` of it.
 template <int TYPE>
-__device__ __forceinline__ void dequant32(uint32_t tile, int r, int kq, uint4 (&out)[4]) {
+__device__ __forceinline__ void dequant16(uint32_t tile, int r, int kq, int sub, uint4 (&out)[2]) {
     const int g = r & 7, rs = r >> 3;
-    if constexpr (TYPE == kQ4_0) {  // (q - 8) * d, dequant.go:83-115
+    if constexpr (TYPE == kQ4_0) {  // (q - 8) * d, dequant.go:83-115; low nibbles = values 0..15
         const int t = kq >> 1, bp = kq & 1;
         const float d = h16(lds16(tile + r * 16 + kq * 2));
         const uint4 q = lds128(tile + 256 + (2 * bp + rs) * 512 + (4 * g + t) * 16);
-        out[0] = nibble_chunk<false>(q.x, q.y, d, -1032.0f * d);
-        out[1] = nibble_chunk<false>(q.z, q.w, d, -1032.0f * d);
-        out[2] = nibble_chunk<true>(q.x, q.y, d, -72.0f * d);
-        out[3] = nibble_chunk<true>(q.z, q.w, d, -72.0f * d);
+        if (sub) {
+            out[0] = nibble_chunk<true>(q.x, q.y, d, -72.0f * d);
+            out[1] = nibble_chunk<true>(q.z, q.w, d, -72.0f * d);
+        } else {
+            out[0] = nibble_chunk<false>(q.x, q.y, d, -1032.0f * d);
+            out[1] = nibble_chunk<false>(q.z, q.w, d, -1032.0f * d);
+        }
     } else if constexpr (TYPE == kQ8_0) {  // q * d, dequant.go:58-78
         const int t = kq >> 1, bp = kq & 1;
         const float d = h16(lds16(tile + r * 16 + kq * 2));
-        const uint4 a = lds128(tile + 256 + (2 * (2 * bp) + rs) * 512 + (4 * g + t) * 16);
-        const uint4 b = lds128(tile + 256 + (2 * (2 * bp + 1) + rs) * 512 + (4 * g + t) * 16);
+        const uint4 a = lds128(tile + 256 + (2 * (2 * bp + sub) + rs) * 512 + (4 * g + t) * 16);
         const float o = -1152.0f * d;  // codes are read as 1024 + (q + 128)
         out[0] = byte_chunk(a.x ^ 0x80808080u, a.y ^ 0x80808080u, d, o);
         out[1] = byte_chunk(a.z ^ 0x80808080u, a.w ^ 0x80808080u, d, o);
-        out[2] = byte_chunk(b.x ^ 0x80808080u, b.y ^ 0x80808080u, d, o);
-        out[3] = byte_chunk(b.z ^ 0x80808080u, b.w ^ 0x80808080u, d, o);
     } else if constexpr (TYPE == kQ4_K) {  // (d*sc)*q - dmin*m
         const int G = kq >> 1, hi = kq & 1;
         const uint4 h = lds128(tile + r * 16);
@@ -221,41 +227,33 @@ __device__ __forceinline__ void dequant32(uint32_t tile, int r, int kq, uint4 (&
             mn = ((s8b >> (8 * j + 4)) & 0x0Fu) | (((s47 >> (8 * j + 6)) & 3u) << 4);
         }
         const float ds = d * (float)sc, dm = dmin * (float)mn;
-        const uint4 q0 = lds128(tile + 256 + rs * 512 + (4 * g + G) * 16);
-        const uint4 q1 = lds128(tile + 256 + (2 + rs) * 512 + (4 * g + G) * 16);
+        const uint4 q = lds128(tile + 256 + (2 * sub + rs) * 512 + (4 * g + G) * 16);
         if (hi) {
             const float o = fmaf(-64.0f, ds, -dm);
-            out[0] = nibble_chunk<true>(q0.x, q0.y, ds, o);
-            out[1] = nibble_chunk<true>(q0.z, q0.w, ds, o);
-            out[2] = nibble_chunk<true>(q1.x, q1.y, ds, o);
-            out[3] = nibble_chunk<true>(q1.z, q1.w, ds, o);
+            out[0] = nibble_chunk<true>(q.x, q.y, ds, o);
+            out[1] = nibble_chunk<true>(q.z, q.w, ds, o);
         } else {
             const float o = fmaf(-1024.0f, ds, -dm);
-            out[0] = nibble_chunk<false>(q0.x, q0.y, ds, o);
-            out[1] = nibble_chunk<false>(q0.z, q0.w, ds, o);
-            out[2] = nibble_chunk<false>(q1.x, q1.y, ds, o);
-            out[3] = nibble_chunk<false>(q1.z, q1.w, ds, o);
+            out[0] = nibble_chunk<false>(q.x, q.y, ds, o);
+            out[1] = nibble_chunk<false>(q.z, q.w, ds, o);
         }
-    } else {  // Q6_K: (d*sc)*(q - 32); values 32kq .. 32kq+31 = 128n + 32c + l
-        const int n = kq >> 2, c = kq & 3, part = c & 1;
+    } else {  // Q6_K: (d*sc)*(q - 32); values 32kq + 16sub + 0..15 = 128n + 32c + 16lh + l
+        const int n = kq >> 2, c = kq & 3, part = c & 1, lh = sub;
         const float d = h16(lds16(tile + 3328 + r * 2));
+        const int lane = 4 * g + 2 * n + lh;
+        const uint4 ql = lds128(tile + 256 + (2 * part + rs) * 512 + lane * 16);
+        const uint4 qh = lds128(tile + 256 + (4 + rs) * 512 + lane * 16);
+        const int sc = (int)(int8_t)lds8(tile + r * 16 + 8 * n + 2 * c + lh);
+        const float ds = d * (float)sc, o = -1056.0f * ds;  // codes are read as 1024 + q
+        const uint32_t lw[4] = {ql.x, ql.y, ql.z, ql.w}, hw[4] = {qh.x, qh.y, qh.z, qh.w};
+        uint32_t code[4];
 #pragma unroll
-        for (int lh = 0; lh < 2; lh++) {
-            const int lane = 4 * g + 2 * n + lh;
-            const uint4 ql = lds128(tile + 256 + (2 * part + rs) * 512 + lane * 16);
-            const uint4 qh = lds128(tile + 256 + (4 + rs) * 512 + lane * 16);
-            const int sc = (int)(int8_t)lds8(tile + r * 16 + 8 * n + 2 * c + lh);
-            const float ds = d * (float)sc, o = -1056.0f * ds;  // codes are read as 1024 + q
-            const uint32_t lw[4] = {ql.x, ql.y, ql.z, ql.w}, hw[4] = {qh.x, qh.y, qh.z, qh.w};
-            uint32_t code[4];
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const uint32_t nib = (c < 2 ? lw[i] : (lw[i] >> 4)) & 0x0F0F0F0Fu;
-                code[i] = nib | (((hw[i] >> (2 * c)) & 0x03030303u) << 4);
-            }
-            out[2 * lh] = byte_chunk(code[0], code[1], ds, o);
-            out[2 * lh + 1] = byte_chunk(code[2], code[3], ds, o);
+        for (int i = 0; i < 4; i++) {
+            const uint32_t nib = (c < 2 ? lw[i] : (lw[i] >> 4)) & 0x0F0F0F0Fu;
+            code[i] = nib | (((hw[i] >> (2 * c)) & 0x03030303u) << 4);
         }
+        out[0] = byte_chunk(code[0], code[1], ds, o);
+        out[1] = byte_chunk(code[2], code[3], ds, o);
     }
 }
 
@@ -263,6 +261,7 @@ template <int TYPE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
     using F = Fmt<TYPE>;
+    constexpr int SA = Depth<TYPE>::SA, SB = Depth<TYPE>::SB, SP = Depth<TYPE>::SP;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // carve: A stages | B stages | packed stages | barriers | tmem slot   (A/B need 1024-byte alignment)
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -299,22 +298,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p
     const uint32_t tmem_d = *tmem_slot_ptr;
 
     if (warp == 0) {
-        if (lane == 0) {
-            // producer: packed weights every 4th stage, activations every stage
+        if (lane == 0) {  // activation producer
             for (int64_t ks = 0; ks < nstages; ks++) {
-                if ((ks & 3) == 0) {
-                    const int64_t kt = ks >> 2;
-                    const int sp = (int)(kt % SP);
-                    if (!mbar_wait(p_empty + 8 * sp, (uint32_t)(((kt / SP) & 1) ^ 1), p.status)) break;
-                    mbar_expect_tx(p_full + 8 * sp, nrt * F::TILE);
-                    for (int i = 0; i < nrt; i++)
-                        bulk_load(p_s + sp * P_BYTES + i * F::TILE, p.tiles + ((rt0 + i) * p.kt + kt) * (int64_t)F::TILE,
-                                  F::TILE, p_full + 8 * sp);
-                }
                 const int sa = (int)(ks % SA);
                 if (!mbar_wait(a_empty + 8 * sa, (uint32_t)(((ks / SA) & 1) ^ 1), p.status)) break;
                 mbar_expect_tx(a_full + 8 * sa, A_BYTES);
                 tma_load_2d(a_s + sa * A_BYTES, &xmap, (int)(ks * BK), (int)m0, a_full + 8 * sa);
+            }
+        }
+    } else if (warp == 2) {
+        if (lane == 0) {  // packed-weight producer: one stage = the 8 row tiles of this column tile
+            for (int64_t kt = 0; kt < p.kt; kt++) {
+                const int sp = (int)(kt % SP);
+                if (!mbar_wait(p_empty + 8 * sp, (uint32_t)(((kt / SP) & 1) ^ 1), p.status)) break;
+                mbar_expect_tx(p_full + 8 * sp, nrt * F::TILE);
+                for (int i = 0; i < nrt; i++)
+                    bulk_load(p_s + sp * P_BYTES + i * F::TILE, p.tiles + ((rt0 + i) * p.kt + kt) * (int64_t)F::TILE,
+                              F::TILE, p_full + 8 * sp);
             }
         }
     } else if (warp == 1) {
@@ -334,8 +334,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p
             umma_commit(d_full);
         }
     } else {
-        // dequantize: thread = (weight row n of the tile, half of the 64-wide stage)
-        const int dt = threadIdx.x - 64, n = dt & 127, half = dt >> 7;
+        // dequantize: thread = (weight row n of the tile, quarter qq of every 64-wide stage).  All four
+        // stages of a packed tile are converted into registers first, so the packed slot is released
+        // early and the wait for a free B stage does not delay the arithmetic.
+        const int dt = threadIdx.x - 32 * kFirstDequantWarp, n = dt & 127, qq = dt >> 7;
         const int rtile = n >> 4, r = n & 15;
         const bool row_exists = rtile < nrt;
         bool ok = true;
@@ -343,35 +345,37 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p
             const int sp = (int)(kt % SP);
             ok = mbar_wait(p_full + 8 * sp, (uint32_t)((kt / SP) & 1), p.status);
             const uint32_t tile = p_s + sp * P_BYTES + rtile * F::TILE;
-            for (int q = 0; q < 4 && ok; q++) {
+            uint4 out[4][2];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                if (row_exists) {
+                    dequant16<TYPE>(tile, r, 2 * q + (qq >> 1), qq & 1, out[q]);
+                } else {
+                    out[q][0] = out[q][1] = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_empty + 8 * sp);
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
                 const int64_t ks = kt * 4 + q;
                 const int sb = (int)(ks % SB);
-                uint4 out[4];
-                if (row_exists) {
-                    dequant32<TYPE>(tile, r, 2 * q + half, out);
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 4; c++) out[c] = make_uint4(0u, 0u, 0u, 0u);
-                }
-                ok = mbar_wait(b_empty + 8 * sb, (uint32_t)(((ks / SB) & 1) ^ 1), p.status);
+                if (ok) ok = mbar_wait(b_empty + 8 * sb, (uint32_t)(((ks / SB) & 1) ^ 1), p.status);
                 const uint32_t rowbase = b_s + sb * B_BYTES + n * 128;
-#pragma unroll
-                for (int c = 0; c < 4; c++) sts128(rowbase + (((4 * half + c) ^ (n & 7)) << 4), out[c]);
+                sts128(rowbase + (((2 * qq) ^ (n & 7)) << 4), out[q][0]);
+                sts128(rowbase + (((2 * qq + 1) ^ (n & 7)) << 4), out[q][1]);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(b_full + 8 * sb);
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(p_empty + 8 * sp);
         }
         // epilogue: TMEM lane = batch row, column = weight row.  Warp w may read lanes 32*(w%4)..+31.
         if (mbar_wait(d_full, 0, p.status)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int quarter = warp & 3, colhalf = (warp - 2) >> 2;
+            const int quarter = warp & 3, colq = (warp - kFirstDequantWarp) >> 2;  // 16 warps: 4 lane quarters x 4 column quarters
             const int64_t row = m0 + quarter * 32 + lane;
-#pragma unroll 1
-            for (int cc = 0; cc < 2; cc++) {
-                const int col0 = colhalf * 64 + cc * 32;
+            {
+                const int col0 = colq * 32;
                 uint32_t v[32];
                 tmem_ld32(tmem_d + ((uint32_t)(quarter * 32) << 16) + col0, v);
                 if (row < p.m) {
@@ -437,6 +441,7 @@ int launch_gemm_t(const Weight &w, const __nv_bfloat16 *x, int64_t m, const floa
     GemmParams p{};
     p.tiles = w.tiles, p.bias = bias, p.y = y, p.status = w.status;
     p.m = m, p.n = w.n, p.y_ld = y_ld, p.rt = w.rt, p.kt = w.kt, p.act = act;
+    constexpr int SA = Depth<TYPE>::SA, SB = Depth<TYPE>::SB, SP = Depth<TYPE>::SP;
     const size_t smem = 1024 + SA * BM * BK * 2 + SB * BN * BK * 2 + SP * 8 * F::TILE + 8 * (2 * SA + 2 * SB + 2 * SP + 1) + 16;
     auto kern = gemm_tcgen05_kernel<TYPE>;
     static thread_local bool configured[16] = {};
