@@ -225,6 +225,23 @@ int b200q_dense(b200q_weight_t h, const void *x_dev, int x_dtype, int64_t m, con
     return launch_gemm(*w, x_dev, x_dtype, m, bias_dev, activation, y_dev, y_ld, s);
 }
 
+int b200q_dense_f32_prefill_noalloc(b200q_weight_t h, const float *x_dev, int64_t m, const float *bias_dev,
+                                    int activation, float *y_dev, int64_t y_ld, void *stream) {
+    auto w = find(h);
+    if (!w) return fail(B200Q_EHANDLE, "dense_noalloc: unknown handle");
+    if (m <= 16) return fail(B200Q_EINVAL, "dense_noalloc: this entry point is the prefill path, m must exceed 16");
+    if (!x_dev || !y_dev) return fail(B200Q_EINVAL, "dense_noalloc: null x or y");
+    if (activation < B200Q_ACT_NONE || activation > B200Q_ACT_TANH) return fail(B200Q_EINVAL, "dense_noalloc: bad activation");
+    if (y_ld == 0) y_ld = w->n;
+    if (y_ld < w->n) return fail(B200Q_EINVAL, "dense_noalloc: y_ld smaller than N");
+    if (reinterpret_cast<uintptr_t>(x_dev) & 15) return fail(B200Q_EINVAL, "dense_noalloc: x must be 16-byte aligned");
+    B200Q_CUDA(cudaSetDevice(w->device));
+    g_last_kernel = B200Q_KERNEL_GEMM_TCGEN05;
+    return launch_gemm_f32_static(*w, x_dev, m, bias_dev, activation, y_dev, y_ld, static_cast<cudaStream_t>(stream));
+}
+
+int64_t b200q_noalloc_capacity(void) { return static_scratch_capacity_elems(); }
+
 int b200q_embedding_lookup(b200q_weight_t h, const int32_t *idx_dev, int64_t n_idx, float *out_dev, void *stream) {
     auto w = find(h);
     if (!w) return fail(B200Q_EHANDLE, "embedding_lookup: unknown handle");

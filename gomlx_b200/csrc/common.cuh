@@ -46,6 +46,11 @@ int launch_gemv(const Weight &w, const void *x, int x_dtype, int m, const float 
 int launch_gemm(const Weight &w, const void *x, int x_dtype, int64_t m, const float *bias, int act, float *y,
                 int64_t y_ld, cudaStream_t s);
 
+// gemm_tcgen05.cu: prefill for f32 activations whose bf16 copy lives in a fixed device array
+int launch_gemm_f32_static(const Weight &w, const float *x, int64_t m, const float *bias, int act, float *y, int64_t y_ld,
+                           cudaStream_t s);
+int64_t static_scratch_capacity_elems();
+
 // Fused epilogue: compute.ActivationType semantics (ml/layers/activation/activation.go:91-121,195-244).
 __device__ __forceinline__ float apply_activation(int act, float v) {
     switch (act) {

@@ -24,6 +24,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <string>
 
 namespace b200q {
 namespace {
@@ -479,6 +480,66 @@ int launch_gemm(const Weight &w, const void *x, int x_dtype, int64_t m, const fl
     }
     if (scratch) cudaFreeAsync(scratch, s);
     return rc;
+}
+
+// ---------------------------------------------------------------------------------------
+// Allocation-free prefill for f32 activations.
+//
+// Some hosts cannot call the CUDA allocator when they need a prefill: a serving loop that runs
+// inside a latency-critical section with allocation forbidden, a process whose memory pool has been
+// handed over entirely to another runtime, or code running under a stream capture whose owner does
+// not allow memory nodes.  For them the bf16 copy of the activations lives in a fixed device array
+// that is part of the library image instead of a stream-ordered allocation.
+//
+// The array costs kStaticScratchBytes of device memory on every GPU that loads the library, from
+// load until the process exits.  All calls on a device share it and it keeps whatever the last call
+// wrote; a call overwrites exactly the m*K elements it reads, so nothing needs clearing, but two calls
+// that overlap on the GPU (different streams, no ordering between them) would race on it.
+// ---------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = 8u << 20;  // 4 Mi bf16 activations, e.g. m*K = 512 x 8192
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+int64_t static_scratch_capacity_elems() { return (int64_t)(kStaticScratchBytes / sizeof(__nv_bfloat16)); }
+
+// Device address of the array on the current device.  The name `g_static_scratch` in host code is only
+// a handle for the runtime, not a device pointer, so the address is asked for once per device (with
+// that device current) and remembered.  This look-up is the set-up step of the first call on a device.
+static int static_scratch_ptr(int device, __nv_bfloat16 **out) {
+    static std::mutex mu;
+    static __nv_bfloat16 *ptrs[64] = {};
+    if (device < 0 || device >= 64) return fail(B200Q_EINVAL, "dense_noalloc: device index out of range");
+    std::lock_guard<std::mutex> lk(mu);
+    if (ptrs[device] == nullptr) {
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
+        if (p == nullptr) return fail(B200Q_ECUDA, "dense_noalloc: static scratch has no device address");
+        ptrs[device] = static_cast<__nv_bfloat16 *>(p);
+    }
+    *out = ptrs[device];
+    return 0;
+}
+
+int launch_gemm_f32_static(const Weight &w, const float *x, int64_t m, const float *bias, int act, float *y, int64_t y_ld,
+                           cudaStream_t s) {
+    const int64_t count = m * w.k;
+    if (count > static_scratch_capacity_elems())
+        return fail(B200Q_EINVAL, "dense_noalloc: m*K = " + std::to_string(count) + " exceeds the static scratch capacity of " +
+                                      std::to_string(static_scratch_capacity_elems()) + " elements");
+    __nv_bfloat16 *scratch = nullptr;
+    int rc = static_scratch_ptr(w.device, &scratch);
+    if (rc != 0) return rc;
+    const int64_t blocks = std::min<int64_t>((count / 4 + 255) / 256, 148 * 8);
+    f32_to_bf16_kernel<<<(unsigned)std::max<int64_t>(1, blocks), 256, 0, s>>>(x, scratch, count);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "dense_noalloc: convert launch");
+    switch (w.type) {
+    case kQ4_0: return launch_gemm_t<kQ4_0>(w, scratch, m, bias, act, y, y_ld, s);
+    case kQ8_0: return launch_gemm_t<kQ8_0>(w, scratch, m, bias, act, y, y_ld, s);
+    case kQ4_K: return launch_gemm_t<kQ4_K>(w, scratch, m, bias, act, y, y_ld, s);
+    case kQ6_K: return launch_gemm_t<kQ6_K>(w, scratch, m, bias, act, y, y_ld, s);
+    }
+    return fail(B200Q_ENOTIMPL, "dense_noalloc: unsupported GGML type");
 }
 
 }  // namespace b200q

@@ -123,6 +123,24 @@ int b200q_dequantize(b200q_weight_t w, float *out_dev, void *stream);
 int b200q_dense(b200q_weight_t w, const void *x_dev, int x_dtype, int64_t m, const float *bias_dev, int activation,
                 float *y_dev, int64_t y_ld, void *stream);
 
+/* No counterpart in the reference: an allocation-free form of b200q_dense for prefill (m > 16) with f32
+ * activations.  b200q_dense converts f32 activations to bf16 in a buffer it takes from the CUDA
+ * stream-ordered allocator; callers that must not allocate at that point (a serving loop inside an
+ * allocation-free critical section, a process whose device memory is owned by another runtime's pool,
+ * a capture whose owner forbids memory nodes) use this entry point instead: the bf16 copy goes to a
+ * fixed array inside the library image.  Limits and rules:
+ *   - m * K <= b200q_noalloc_capacity() (4 Mi elements, 8 MiB per GPU, held from library load to
+ *     process exit); larger requests fail with B200Q_EINVAL and launch nothing;
+ *   - the first call on each device looks the array's device address up; make that first call outside
+ *     any stream capture;
+ *   - every call on a device shares the array: calls that may overlap on the GPU (different streams
+ *     without ordering) race on it and must be serialised by the caller.
+ * Arguments and results are those of b200q_dense with x_dtype = B200Q_F32. */
+int b200q_dense_f32_prefill_noalloc(b200q_weight_t w, const float *x_dev, int64_t m, const float *bias_dev,
+                                    int activation, float *y_dev, int64_t y_ld, void *stream);
+/* Largest m * K the entry point above accepts. */
+int64_t b200q_noalloc_capacity(void);
+
 /* compute.Function.QuantizedEmbeddingLookup (core/graph/fused_ops.go:281-309,
  * ml/ggml/gather.go:21-49): out_dev[i, :] = dequant(table[idx[i], :]).  An index
  * outside [0, N) yields B200Q_EINVAL after the launch completes (checked on the
