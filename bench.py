@@ -314,7 +314,13 @@ def run_cuda(args) -> None:
         for w in layer:
             w.free()
     if world > 1:
-        dist.destroy_process_group()
+        # Tearing the NCCL communicator down (destroy_process_group) has been seen to block for
+        # minutes on multi-GPU boxes; every rank is past its last collective here, so leave directly.
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main() -> None:
