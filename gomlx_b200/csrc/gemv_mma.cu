@@ -71,6 +71,7 @@ struct GemvParams {
     int kp;         // k parts per row tile inside a CTA: unit = (row tile, k part)
     int ktp;        // k tiles per part
     int depth;      // ring slots per warp
+    int pre_issue;  // slots requested before the activations are staged (the rest right after)
     int tps;        // tiles per ring slot (one TMA copy)
     int maxunits;   // upper bound on units per CTA (sizes the partial-sum area)
 };
@@ -585,6 +586,9 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
     using F = Fmt<TYPE>;
     extern __shared__ __align__(128) uint8_t smem[];
     B200Q_TRACE_POINT(0);
+    // Programmatic dependent launch: let the next kernel in the stream start its own prologue (barrier
+    // set-up and weight prefetch, which depend on nothing we write) as soon as SM resources free up.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int nwarps = blockDim.x >> 5;
     const int kc = p.kts * F::TK;  // staged K slice (values)
@@ -645,8 +649,10 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
         producer_skip_empty();
     };
     B200Q_TRACE_POINT(6);
+    // `pre_issue` slots are requested before the activations are staged, the rest right after.
+    int issued0 = 0;
     if (lane == 0)
-        for (int d = 0; d < p.depth && prow < nrows; d++) issue_next();
+        for (; issued0 < p.pre_issue && prow < nrows; issued0++) issue_next();
     B200Q_TRACE_POINT(7);
 
     // Lane constants for the staged activations (see XCols).
@@ -669,8 +675,13 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
         }
     }
 
+    // Everything above touched only the immutable weights.  The activations may be the output of the
+    // kernel before us in the stream, and our outputs may overwrite what it still reads: wait for it.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (kt_begin < kt_end) stage_x<TYPE>(p, (int64_t)kt_begin * F::TK, (kt_end - kt_begin) * F::TK, xs_stride, ns, xs, shi, slo);
     __syncthreads();
+    if (lane == 0)
+        for (; issued0 < p.depth && prow < nrows; issued0++) issue_next();
     B200Q_TRACE_POINT(1);
 
     int cd = 0;
@@ -787,7 +798,8 @@ struct Plan {
 // Picks cluster splits S, k parts per row tile KP and warps W.  Cost model: the busiest warp of the
 // busiest CTA sets the time, so minimise its tile count; small penalties for cluster size (barriers,
 // partial-sum traffic) and for leaving SMs idle.
-Plan make_plan(int64_t rt, int64_t kt, int sms, size_t x_bytes_per_ktile, size_t x_limit, size_t unit_red_bytes) {
+Plan make_plan(int64_t rt, int64_t kt, int sms, int max_warps, size_t x_bytes_per_ktile, size_t x_limit,
+               size_t unit_red_bytes, size_t smem_limit) {
     Plan best{1, 1, 1, 1, 1e30};
     for (int s = 1; s <= 8; s *= 2) {
         if (s > kt) break;
@@ -800,14 +812,15 @@ Plan make_plan(int64_t rt, int64_t kt, int sms, size_t x_bytes_per_ktile, size_t
             if (ktp < 2 && kp > 1) break;  // keep at least two tiles per unit
             const int64_t units = rc * kp;
             // staged x plus the per-unit partial sums must leave room for the tile rings
-            if ((size_t)kts * x_bytes_per_ktile + (size_t)units * unit_red_bytes > 150 * 1024 && kp > 1) break;
-            for (int w = 1; w <= kMaxWarps; w++) {
+            if ((size_t)kts * x_bytes_per_ktile + (size_t)units * unit_red_bytes > smem_limit * 2 / 3 && kp > 1) break;
+            for (int w = 1; w <= max_warps; w++) {
                 const int64_t rounds = (units + w - 1) / w;
                 double cost = (double)(rounds * ktp);
-                cost *= 1.0 + 0.03 * (s > 1 ? std::log2((double)s) : 0.0);
+                cost *= s == 1 ? 1.0 : s == 2 ? 1.1 : s == 4 ? 1.6 : 2.2;  // measured: wide clusters schedule poorly
                 cost *= 1.0 + 0.01 * (kp - 1);                       // more partial sums to add
-                cost *= 1.0 + 0.25 * (kMaxWarps - w) / kMaxWarps;    // fewer warps hide less latency
+                cost *= 1.0 + 0.25 * (max_warps - w) / max_warps;      // fewer warps hide less latency
                 cost *= (double)sms / (double)(ncl * s);             // idle SMs
+                cost *= 1.0 + (double)(kts * x_bytes_per_ktile) / (96.0 * 1024.0);  // staging time and ring space
                 if (cost < best.cost) best = Plan{s, ncl, w, kp, cost};
             }
         }
@@ -822,11 +835,22 @@ int launch_t(const Weight &w, const GemvParams &p0, cudaStream_t s) {
     int dev_sms = 148;
     cudaDeviceGetAttribute(&dev_sms, cudaDevAttrMultiProcessorCount, w.device);
 
+    // Two CTAs of up to 8 warps per SM (half the shared memory each) when the staged activations are
+    // small: finer load balance, and a dependent launch can move into an SM as soon as one CTA leaves.
     const size_t x_per_ktile = (size_t)p.m * (F::TK * 2 + (F::SUB ? 4 * (F::TK / F::SUB) : 0));
-    Plan plan = make_plan(w.rt, w.kt, dev_sms, x_per_ktile, (size_t)env_int("B200Q_GEMV_XSMEM", 96 * 1024),
-                          (size_t)NB * 128 * sizeof(float));
+    const size_t x_whole = x_per_ktile * (size_t)w.kt;
+    int cps = 1;
+    (void)x_whole;
+    cps = std::max(1, std::min(2, env_int("B200Q_GEMV_CPS", cps)));
+    const size_t smem_limit = cps == 2 ? 112 * 1024 : kSmemLimit;
+    const int max_warps = cps == 2 ? 8 : kMaxWarps;
+    const int slots = dev_sms * cps;
+
+    Plan plan = make_plan(w.rt, w.kt, slots, max_warps, x_per_ktile,
+                          (size_t)env_int("B200Q_GEMV_XSMEM", cps == 2 ? 32 * 1024 : 136 * 1024),
+                          (size_t)NB * 128 * sizeof(float), smem_limit);
     plan.splits = std::max(1, std::min<int>({8, (int)w.kt, env_int("B200Q_GEMV_SPLITS", plan.splits)}));
-    if (std::getenv("B200Q_GEMV_SPLITS")) plan.nclusters = (int)std::max<int64_t>(1, std::min<int64_t>(dev_sms / plan.splits, w.rt));
+    if (std::getenv("B200Q_GEMV_SPLITS")) plan.nclusters = (int)std::max<int64_t>(1, std::min<int64_t>(slots / plan.splits, w.rt));
     plan.nclusters = (int)std::max<int64_t>(1, std::min<int64_t>(env_int("B200Q_GEMV_CLUSTERS", plan.nclusters), w.rt));
     p.splits = 1;
     p.split_shift = 0;
@@ -836,7 +860,7 @@ int launch_t(const Weight &w, const GemvParams &p0, cudaStream_t s) {
     p.rows_q = (int)(w.rt / p.nclusters), p.rows_r = (int)(w.rt % p.nclusters);
     p.kp = std::max(1, std::min(p.kts, env_int("B200Q_GEMV_KP", plan.kp)));
     p.ktp = (p.kts + p.kp - 1) / p.kp;
-    int warps = std::max(1, std::min(kMaxWarps, env_int("B200Q_GEMV_WARPS", plan.warps)));
+    int warps = std::max(1, std::min(max_warps, env_int("B200Q_GEMV_WARPS", plan.warps)));
     const int64_t rows_per_cluster = (w.rt + p.nclusters - 1) / p.nclusters;
     p.maxunits = (int)(rows_per_cluster * p.kp);
     p.tps = std::max(1, std::min(p.ktp, env_int("B200Q_GEMV_TPS", F::TILE <= 2304 ? 2 : 1)));
@@ -849,7 +873,7 @@ int launch_t(const Weight &w, const GemvParams &p0, cudaStream_t s) {
     int depth = 0;
     for (;; warps--) {  // shrink the CTA until every warp gets at least two ring slots
         const size_t bar_bytes = (size_t)warps * 8 * 8;
-        depth = fixed + bar_bytes < kSmemLimit ? (int)((kSmemLimit - fixed - bar_bytes) / ((size_t)warps * slot_bytes)) : 0;
+        depth = fixed + bar_bytes < smem_limit ? (int)((smem_limit - fixed - bar_bytes) / ((size_t)warps * slot_bytes)) : 0;
         if (depth >= 2 || warps == 1) break;
     }
     if (depth < 1) return fail(B200Q_EINVAL, "gemv: K is too large for the shared-memory staging of this batch size");
@@ -857,6 +881,7 @@ int launch_t(const Weight &w, const GemvParams &p0, cudaStream_t s) {
     depth = (int)std::max<int64_t>(1, std::min<int64_t>({(int64_t)depth, (int64_t)8, slots_per_warp}));
     depth = std::max(1, std::min(depth, env_int("B200Q_GEMV_DEPTH", depth)));
     p.depth = depth;
+    p.pre_issue = std::max(1, std::min(depth, env_int("B200Q_GEMV_PRE", depth)));
     const size_t smem = fixed + (size_t)warps * depth * slot_bytes + (size_t)warps * depth * 8;
 
     auto kern = gemv_mma_kernel<TYPE, NB>;
@@ -870,13 +895,15 @@ int launch_t(const Weight &w, const GemvParams &p0, cudaStream_t s) {
     cfg.blockDim = dim3(warps * 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = p.splits;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = env_int("B200Q_GEMV_PDL", 1) ? 2 : 1;
     B200Q_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
     return 0;
 }
