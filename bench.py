@@ -186,19 +186,53 @@ def run_cuda(args) -> None:
                         for w, (_, t, _, _, _) in zip(packed, PROJECTIONS)])
     local_bytes = sum(w.device_bytes for layer in weights for w in layer)
 
+    # N > 1: the all-gather of every projection's output is fused into the GEMV epilogue (peer stores
+    # over NVLink into one symmetric buffer per rank); NCCL all-gather is the fallback / comparison.
+    gather = "none" if world == 1 else args.gather
+    peer_layers = None
+    if gather == "peer":
+        try:
+            from gomlx_b200.sharded import PeerScatterBuffers, PeerScatterDense
+            per_layer = sum(n for _, _, n, _, _ in PROJECTIONS) * batch
+            bufs = PeerScatterBuffers(LAYERS * per_layer, local)
+            peer_layers, off = [], 0
+            for li in range(LAYERS):
+                row = []
+                for pi, (_, t, n, _, _) in enumerate(PROJECTIONS):
+                    row.append(PeerScatterDense(weights[li][pi], quant[t], bufs, off, batch, local, n_total=n))
+                    off += batch * n
+                peer_layers.append(row)
+        except Exception as e:  # symmetric memory unavailable: fall back to NCCL
+            print(f"[bench] peer scatter unavailable ({e!r}); using NCCL all-gather", file=sys.stderr)
+            gather, peer_layers = "nccl", None
+
     gen = torch.Generator(device="cpu").manual_seed(1234)
     x_host = {k: torch.randn(batch, k, generator=gen).pin_memory() for k in (4096, 14336)}
     x_dev = {k: v.to(dev) for k, v in x_host.items()}
     y_loc = [[torch.empty(batch, w.n, device=dev) for w in layer] for layer in weights]
-    y_full = [[torch.empty(world * batch, w.n, device=dev) for w in layer] for layer in weights] if world > 1 else y_loc
+    if gather == "peer":
+        y_full = [[d.y for d in row] for row in peer_layers]
+    elif gather == "nccl":
+        y_full = [[torch.empty(world * batch, w.n, device=dev) for w in layer] for layer in weights]
+    else:
+        y_full = y_loc
     y_host = torch.empty_like(y_full[-1][-1], device="cpu").pin_memory()
+
+    act_types = {"none": g.Activation.NONE, "silu": g.Activation.SILU}
+    # ranks are ordered where a real decoder layer consumes gathered outputs: after q/k/v, o, gate/up, down
+    sync_after = {"v", "o", "up", "down"}
 
     def step():
         for li in range(LAYERS):
-            for pi, (_, t, _, k, act) in enumerate(PROJECTIONS):
-                g.backend_fused_quantized_dense(x_dev[k], weights[li][pi], None, quant[t], acts[act], out=y_loc[li][pi])
-                if world > 1:
-                    dist.all_gather_into_tensor(y_full[li][pi], y_loc[li][pi])
+            for pi, (name, t, _, k, act) in enumerate(PROJECTIONS):
+                if gather == "peer":
+                    peer_layers[li][pi](x_dev[k], None, act_types[act])
+                    if name in sync_after:
+                        bufs.barrier()
+                else:
+                    g.backend_fused_quantized_dense(x_dev[k], weights[li][pi], None, quant[t], acts[act], out=y_loc[li][pi])
+                    if gather == "nccl":
+                        dist.all_gather_into_tensor(y_full[li][pi], y_loc[li][pi])
 
     def select(pred):
         def run():
@@ -290,7 +324,9 @@ def run_cuda(args) -> None:
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f16 multiply / f32 accumulate on packed u8 blocks", "data": "synthetic",
         "config": {"workload": WORKLOAD, "batch": batch, "weight_bytes_per_step": total_bytes,
-                   "parallelism": f"rows/{world}" + (" + NCCL all-gather per projection" if world > 1 else ""),
+                   "parallelism": f"rows/{world}" + {"none": "", "nccl": " + NCCL all-gather per projection",
+                                                           "peer": " + all-gather fused into the GEMV epilogue (NVLink peer stores), "
+                                                                   "4 device barriers per layer"}[gather],
                    "inputs": "fixed N(0,1) activations per projection (outputs not chained)",
                    "l2": f"no flush: {local_bytes / 1e6:.0f} MB of weights per GPU per step exceed the 126 MB L2",
                    "launch": "one CUDA graph of 224 GEMV launches per step"},
@@ -331,6 +367,7 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"], help="N > 1: how outputs are all-gathered")
     ap.add_argument("--traffic", type=float, default=None, help="dram bytes per launch of the dominant kernel (ncu)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -225,6 +225,24 @@ int b200q_dense(b200q_weight_t h, const void *x_dev, int x_dtype, int64_t m, con
     return launch_gemm(*w, x_dev, x_dtype, m, bias_dev, activation, y_dev, y_ld, s);
 }
 
+int b200q_dense_scatter(b200q_weight_t h, const void *x_dev, int x_dtype, int64_t m, const float *bias_dev, int activation,
+                        float *y_local, float *const *y_peers, int n_peers, int64_t y_ld, int64_t row_offset, void *stream) {
+    auto w = find(h);
+    if (!w) return fail(B200Q_EHANDLE, "dense_scatter: unknown handle");
+    if (m == 0) return B200Q_OK;
+    if (m < 0 || m > 16) return fail(B200Q_ENOTIMPL, "dense_scatter: only the decode path (m <= 16) scatters to peers");
+    if (!x_dev || !y_local) return fail(B200Q_EINVAL, "dense_scatter: null x or y");
+    if (x_dtype != B200Q_F32 && x_dtype != B200Q_BF16) return fail(B200Q_EINVAL, "dense_scatter: x dtype must be f32 or bf16");
+    if (activation < B200Q_ACT_NONE || activation > B200Q_ACT_TANH) return fail(B200Q_EINVAL, "dense_scatter: bad activation");
+    if (n_peers < 0 || n_peers > 7) return fail(B200Q_EINVAL, "dense_scatter: at most 7 peers");
+    if (row_offset < 0 || y_ld < row_offset + w->n) return fail(B200Q_EINVAL, "dense_scatter: y_ld smaller than row_offset + N");
+    if (reinterpret_cast<uintptr_t>(x_dev) & 15) return fail(B200Q_EINVAL, "dense_scatter: x must be 16-byte aligned");
+    B200Q_CUDA(cudaSetDevice(w->device));
+    g_last_kernel = B200Q_KERNEL_GEMV_MMA;
+    return launch_gemv(*w, x_dev, x_dtype, (int)m, bias_dev, activation, y_local, y_ld, static_cast<cudaStream_t>(stream),
+                       y_peers, n_peers, row_offset);
+}
+
 int b200q_dense_f32_prefill_noalloc(b200q_weight_t h, const float *x_dev, int64_t m, const float *bias_dev,
                                     int activation, float *y_dev, int64_t y_ld, void *stream) {
     auto w = find(h);

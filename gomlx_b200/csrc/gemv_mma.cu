@@ -59,8 +59,11 @@ struct GemvParams {
     const void *x;
     const float *bias;
     float *y;
+    float *y_peer[7];  // the same output buffer on the other GPUs of a row-sharded layer (NVLink peer memory)
+    int npeers;        // number of valid entries in y_peer
     int *status;
     int64_t n, k, y_ld;
+    int64_t row_off;   // first output column of this shard inside the full [m, N_total] result
     int64_t rt, kt;  // row tiles (16 rows) and k tiles (256 values) of the weight
     int m, x_dtype, act;
     int splits;     // CTAs per cluster (power of two); split s owns k tiles [s*kts, (s+1)*kts)
@@ -765,7 +768,13 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
                 }
             }
             if (p.bias != nullptr) v += __ldg(p.bias + row);
-            p.y[(int64_t)col * p.y_ld + row] = apply_activation(p.act, v);
+            // The finished value goes to this GPU's buffer and, for a row-sharded layer, straight into the
+            // buffer of every peer GPU (plain stores over NVLink): the all-gather of the outputs happens
+            // in the epilogue, tile by tile, instead of in a collective after the kernel.
+            const float out = apply_activation(p.act, v);
+            const int64_t at = (int64_t)col * p.y_ld + p.row_off + row;
+            p.y[at] = out;
+            for (int pr = 0; pr < p.npeers; pr++) p.y_peer[pr][at] = out;
         }
     }
     if (p.splits > 1) cluster.sync();  // keep shared memory alive until every peer has read it
@@ -916,13 +925,17 @@ int launch_nb(const Weight &w, const GemvParams &p, cudaStream_t s) {
 }  // namespace
 
 int launch_gemv(const Weight &w, const void *x, int x_dtype, int m, const float *bias, int act, float *y, int64_t y_ld,
-                cudaStream_t s) {
+                cudaStream_t s, float *const *y_peers, int npeers, int64_t row_off) {
     if (m < 1 || m > 16) return fail(B200Q_EINVAL, "gemv: m must be in 1..16");
+    if (npeers < 0 || npeers > 7 || (npeers > 0 && y_peers == nullptr)) return fail(B200Q_EINVAL, "gemv: bad peer list");
     GemvParams p{};
     p.tiles = w.tiles;
     p.x = x;
     p.bias = bias;
     p.y = y;
+    for (int i = 0; i < npeers; i++) p.y_peer[i] = y_peers[i];
+    p.npeers = npeers;
+    p.row_off = row_off;
     p.n = w.n, p.k = w.k, p.y_ld = y_ld;
     p.rt = w.rt, p.kt = w.kt;
     p.m = m, p.x_dtype = x_dtype, p.act = act;

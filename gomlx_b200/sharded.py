@@ -74,3 +74,70 @@ class ShardedQuantizedDense:
     def free(self) -> None:
         if isinstance(self.local, ResidentWeight):
             self.local.free()
+
+
+class PeerScatterBuffers:
+    """One symmetric-memory buffer per rank, mapped into every rank of ``group`` (CUDA peer memory over
+    NVLink), for layers whose kernels write their output slice straight into all peers.
+
+    ``floats`` float32 values are allocated on every rank; ``ptr(rank, offset)`` is the device address,
+    in this process, of element ``offset`` of ``rank``'s buffer, and ``local`` is this rank's buffer as a
+    tensor.  ``barrier()`` enqueues a device-side barrier of all ranks on the current stream: after it,
+    every store issued before it on any rank is visible to every rank.
+    """
+
+    def __init__(self, floats: int, device: int, group: Optional[dist.ProcessGroup] = None):
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.local = symm_mem.empty(floats, dtype=torch.float32, device=torch.device("cuda", device))
+        self.handle = symm_mem.rendezvous(self.local, group.group_name)
+        self._ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.local.zero_()
+
+    def ptr(self, rank: int, offset: int = 0) -> int:
+        return self._ptrs[rank] + 4 * offset
+
+    def barrier(self) -> None:
+        self.handle.barrier(channel=0)
+
+
+class PeerScatterDense:
+    """Row-sharded decode dense whose all-gather is fused into the GEMV epilogue: each rank's kernel
+    stores its slice of ``y`` into its own and every peer's result buffer (``b200q_dense_scatter``).
+    The result region is ``[max_m, N_total]`` float32 at ``offset`` of a shared ``PeerScatterBuffers``;
+    call ``buffers.barrier()`` before any rank reads it."""
+
+    def __init__(self, weights, quant: Quantization, buffers: PeerScatterBuffers, offset: int, max_m: int, device: int,
+                 n_total: Optional[int] = None):
+        """``weights``: the full packed matrix (this rank's rows are uploaded), or a ResidentWeight that
+        already holds this rank's shard together with ``n_total``."""
+        import ctypes
+        self.quant, self.buffers, self.offset, self.max_m = quant, buffers, offset, max_m
+        if isinstance(weights, ResidentWeight):
+            self.local, self.n_total = weights, int(n_total if n_total is not None else weights.n_total)
+        else:
+            self.n_total = int(weights.shape[0])
+            self.local = upload(weights, quant.ggml_type, device, shard=(buffers.rank, buffers.world))
+        peers = [buffers.ptr(r, offset) for r in range(buffers.world) if r != buffers.rank]
+        self._peer_arr = (ctypes.c_void_p * max(1, len(peers)))(*peers)
+        self._n_peers = len(peers)
+        self.y = buffers.local[offset:offset + max_m * self.n_total].view(max_m, self.n_total)
+
+    def __call__(self, x: torch.Tensor, bias=None, activation: Activation = Activation.NONE) -> torch.Tensor:
+        import ctypes
+        from . import _native as nat
+        x2 = x.reshape(-1, self.local.k).contiguous()
+        m = x2.shape[0]
+        if m > self.max_m:
+            raise ValueError(f"batch {m} exceeds the {self.max_m} rows reserved for this layer")
+        b = None if bias is None else bias[self.local.row_begin:self.local.row_begin + self.local.n].contiguous()
+        nat.check(nat.lib().b200q_dense_scatter(
+            self.local.handle, ctypes.c_void_p(x2.data_ptr()), nat.F32 if x2.dtype == torch.float32 else nat.BF16, m,
+            ctypes.c_void_p(b.data_ptr()) if b is not None else None, int(activation.to_backend()),
+            ctypes.c_void_p(self.buffers.ptr(self.buffers.rank, self.offset)), self._peer_arr, self._n_peers,
+            self.n_total, self.local.row_begin, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return self.y[:m]
+
+    def free(self) -> None:
+        self.local.free()

@@ -123,6 +123,17 @@ int b200q_dequantize(b200q_weight_t w, float *out_dev, void *stream);
 int b200q_dense(b200q_weight_t w, const void *x_dev, int x_dtype, int64_t m, const float *bias_dev, int activation,
                 float *y_dev, int64_t y_ld, void *stream);
 
+/* Row-sharded decode (m <= 16) with the all-gather of the outputs fused into the kernel.  The
+ * reference's graph layer has no all-gather (only AllReduce, core/graph/distributed.go:217-248); this
+ * is the multi-GPU form of b200q_dense for a weight uploaded as a row shard.  `w` holds rows
+ * [row_offset, row_offset + n) of an [N_total, K] matrix.  Every rank owns one [m, y_ld] f32 result
+ * buffer; y_local is this rank's, y_peers[0..n_peers) are the other ranks' buffers mapped into this
+ * process (CUDA peer / symmetric memory).  The epilogue stores each finished value at column
+ * row_offset + n of y_local and of every peer buffer (plain stores over NVLink).  The caller orders the
+ * ranks (a device-side barrier on the stream) before anyone reads the gathered result. */
+int b200q_dense_scatter(b200q_weight_t w, const void *x_dev, int x_dtype, int64_t m, const float *bias_dev, int activation,
+                        float *y_local, float *const *y_peers, int n_peers, int64_t y_ld, int64_t row_offset, void *stream);
+
 /* No counterpart in the reference: an allocation-free form of b200q_dense for prefill (m > 16) with f32
  * activations.  b200q_dense converts f32 activations to bf16 in a buffer it takes from the CUDA
  * stream-ordered allocator; callers that must not allocate at that point (a serving loop inside an

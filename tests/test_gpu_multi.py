@@ -1,0 +1,70 @@
+"""Row-sharded decode with the all-gather fused into the GEMV epilogue, on two GPUs of one box.
+Skipped where fewer than two GPUs are visible."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import gomlx_b200 as g
+        from gomlx_b200.sharded import PeerScatterBuffers, PeerScatterDense
+        from oracle import oracle as o
+        n, k, max_m = 1024 + 48, 2048, 8
+        quant = g.Quantization(g.QuantizationScheme.GGML, g.GGMLQuantType.Q4_K)
+        w = o.make_weights(o.Q4_K, n, k, seed=1)
+        rng = np.random.default_rng(2)
+        bias = rng.standard_normal(n).astype(np.float32)
+        bufs = PeerScatterBuffers(max_m * n, rank)
+        layer = PeerScatterDense(w, quant, bufs, 0, max_m, rank)
+        for m in (1, 5):
+            x = rng.standard_normal((m, k)).astype(np.float32)
+            y = layer(torch.from_numpy(x).cuda(), torch.from_numpy(bias).cuda(), g.Activation.SILU)
+            bufs.barrier()
+            torch.cuda.synchronize()
+            ref = o.dense(o.Q4_K, w, x, bias, o.ACT_SILU, route="f64")
+            pre = o.dense(o.Q4_K, w, x, bias, 0, route="f64")
+            err = np.abs(y.cpu().numpy() - ref).max() / np.abs(pre).max()
+            assert err <= 3e-3, (rank, m, err)
+            bufs.barrier()  # nobody overwrites the buffers while a peer still reads them
+        q.put((rank, "ok"))
+    except Exception as e:
+        q.put((rank, repr(e)))
+    finally:
+        torch.cuda.synchronize()
+        os._exit(0)  # tearing the NCCL communicator down can block for minutes
+
+
+def test_two_gpu_peer_scatter(oracle):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(30)
+    assert sorted(results) == [(0, "ok"), (1, "ok")], results
