@@ -42,6 +42,25 @@ template <> struct Depth<kQ8_0> { static constexpr int SA = 5, SB = 3, SP = 2; }
 template <> struct Depth<kQ6_K> { static constexpr int SA = 6, SB = 4, SP = 2; };            // 3360-byte tiles
 constexpr int kGemmSpinLimit = 1 << 24;
 
+#ifdef B200Q_TRACE
+// Diagnostic build only: timestamps (ns) of CTA 0, [role][stage][point].
+__device__ unsigned long long *g_gemm_trace = nullptr;
+__device__ __forceinline__ unsigned long long gemm_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define GEMM_TRACE(role, stage, point)                                                                   \
+    do {                                                                                                  \
+        if (g_gemm_trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (stage) < 256)              \
+            g_gemm_trace[((role) * 256 + (stage)) * 4 + (point)] = gemm_now();                            \
+    } while (0)
+#else
+#define GEMM_TRACE(role, stage, point) \
+    do {                               \
+    } while (0)
+#endif
+
 struct GemmParams {
     const uint8_t *tiles;
     const float *bias;
@@ -298,39 +317,54 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = *tmem_slot_ptr;
 
+    // The three single-thread loops below are the pacemakers of the pipeline; they use 32-bit ring
+    // counters and phase bits (no divisions) so that one trip takes tens, not hundreds, of cycles.
+    const int nst = (int)nstages, nkt = (int)p.kt;
     if (warp == 0) {
         if (lane == 0) {  // activation producer
-            for (int64_t ks = 0; ks < nstages; ks++) {
-                const int sa = (int)(ks % SA);
-                if (!mbar_wait(a_empty + 8 * sa, (uint32_t)(((ks / SA) & 1) ^ 1), p.status)) break;
+            uint32_t sa = 0, ph = 1;
+            for (int ks = 0; ks < nst; ks++) {
+                if (!mbar_wait(a_empty + 8 * sa, ph, p.status)) break;
+                GEMM_TRACE(0, ks, 0);
                 mbar_expect_tx(a_full + 8 * sa, A_BYTES);
-                tma_load_2d(a_s + sa * A_BYTES, &xmap, (int)(ks * BK), (int)m0, a_full + 8 * sa);
+                tma_load_2d(a_s + sa * A_BYTES, &xmap, ks * BK, (int)m0, a_full + 8 * sa);
+                if (++sa == SA) sa = 0, ph ^= 1;
             }
         }
     } else if (warp == 2) {
         if (lane == 0) {  // packed-weight producer: one stage = the 8 row tiles of this column tile
-            for (int64_t kt = 0; kt < p.kt; kt++) {
-                const int sp = (int)(kt % SP);
-                if (!mbar_wait(p_empty + 8 * sp, (uint32_t)(((kt / SP) & 1) ^ 1), p.status)) break;
+            uint32_t sp = 0, ph = 1;
+            const uint8_t *src = p.tiles + rt0 * p.kt * (int64_t)F::TILE;
+            const int64_t row_stride = p.kt * (int64_t)F::TILE;
+            for (int kt = 0; kt < nkt; kt++) {
+                if (!mbar_wait(p_empty + 8 * sp, ph, p.status)) break;
                 mbar_expect_tx(p_full + 8 * sp, nrt * F::TILE);
                 for (int i = 0; i < nrt; i++)
-                    bulk_load(p_s + sp * P_BYTES + i * F::TILE, p.tiles + ((rt0 + i) * p.kt + kt) * (int64_t)F::TILE,
-                              F::TILE, p_full + 8 * sp);
+                    bulk_load(p_s + sp * P_BYTES + i * F::TILE, src + i * row_stride, F::TILE, p_full + 8 * sp);
+                src += F::TILE;
+                if (++sp == SP) sp = 0, ph ^= 1;
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            for (int64_t ks = 0; ks < nstages; ks++) {
-                const int sa = (int)(ks % SA), sb = (int)(ks % SB);
-                if (!mbar_wait(a_full + 8 * sa, (uint32_t)((ks / SA) & 1), p.status)) break;
-                if (!mbar_wait(b_full + 8 * sb, (uint32_t)((ks / SB) & 1), p.status)) break;
+            uint32_t sa = 0, pa = 0, sb = 0, pb = 0;
+            const uint64_t ad0 = umma_desc(a_s), bd0 = umma_desc(b_s);
+            for (int ks = 0; ks < nst; ks++) {
+                GEMM_TRACE(1, ks, 0);
+                if (!mbar_wait(a_full + 8 * sa, pa, p.status)) break;
+                GEMM_TRACE(1, ks, 1);
+                if (!mbar_wait(b_full + 8 * sb, pb, p.status)) break;
+                GEMM_TRACE(1, ks, 2);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t ad = umma_desc(a_s + sa * A_BYTES), bd = umma_desc(b_s + sb * B_BYTES);
+                const uint64_t ad = ad0 + ((sa * A_BYTES) >> 4), bd = bd0 + ((sb * B_BYTES) >> 4);
 #pragma unroll
                 for (int k = 0; k < BK / 16; k++)  // +32 bytes along K inside the 128-byte swizzle atom
                     umma_bf16(tmem_d, ad + 2 * k, bd + 2 * k, (ks > 0 || k > 0) ? 1u : 0u);
                 umma_commit(a_empty + 8 * sa);
                 umma_commit(b_empty + 8 * sb);
+                GEMM_TRACE(1, ks, 3);
+                if (++sa == SA) sa = 0, pa ^= 1;
+                if (++sb == SB) sb = 0, pb ^= 1;
             }
             umma_commit(d_full);
         }
@@ -342,14 +376,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p
         const int rtile = n >> 4, r = n & 15;
         const bool row_exists = rtile < nrt;
         bool ok = true;
-        for (int64_t kt = 0; kt < p.kt && ok; kt++) {
-            const int sp = (int)(kt % SP);
-            ok = mbar_wait(p_full + 8 * sp, (uint32_t)((kt / SP) & 1), p.status);
+        uint32_t sp = 0, pp = 0, sb = 0, pb = 1;
+        const uint32_t row_off = n * 128, c0 = ((2 * qq) ^ (n & 7)) << 4, c1 = ((2 * qq + 1) ^ (n & 7)) << 4;
+        for (int kt = 0; kt < nkt && ok; kt++) {
+            ok = mbar_wait(p_full + 8 * sp, pp, p.status);
             const uint32_t tile = p_s + sp * P_BYTES + rtile * F::TILE;
             uint4 out[4][2];
 #pragma unroll
             for (int q = 0; q < 4; q++) {
+#ifdef B200Q_GEMM_FAKE_DEQUANT
+                if (false) {
+#else
                 if (row_exists) {
+#endif
                     dequant16<TYPE>(tile, r, 2 * q + (qq >> 1), qq & 1, out[q]);
                 } else {
                     out[q][0] = out[q][1] = make_uint4(0u, 0u, 0u, 0u);
@@ -357,21 +396,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(p_empty + 8 * sp);
+            if (++sp == SP) sp = 0, pp ^= 1;
 #pragma unroll
             for (int q = 0; q < 4; q++) {
-                const int64_t ks = kt * 4 + q;
-                const int sb = (int)(ks % SB);
-                if (ok) ok = mbar_wait(b_empty + 8 * sb, (uint32_t)(((ks / SB) & 1) ^ 1), p.status);
-                const uint32_t rowbase = b_s + sb * B_BYTES + n * 128;
-                sts128(rowbase + (((2 * qq) ^ (n & 7)) << 4), out[q][0]);
-                sts128(rowbase + (((2 * qq + 1) ^ (n & 7)) << 4), out[q][1]);
+                if (threadIdx.x == 32 * kFirstDequantWarp) GEMM_TRACE(2, kt * 4 + q, 0);
+                if (ok) ok = mbar_wait(b_empty + 8 * sb, pb, p.status);
+                if (threadIdx.x == 32 * kFirstDequantWarp) GEMM_TRACE(2, kt * 4 + q, 1);
+                const uint32_t rowbase = b_s + sb * B_BYTES + row_off;
+                sts128(rowbase + c0, out[q][0]);
+                sts128(rowbase + c1, out[q][1]);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                if (threadIdx.x == 32 * kFirstDequantWarp) GEMM_TRACE(2, kt * 4 + q, 2);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(b_full + 8 * sb);
+                if (threadIdx.x == 32 * kFirstDequantWarp) GEMM_TRACE(2, kt * 4 + q, 3);
+                if (++sb == SB) sb = 0, pb ^= 1;
             }
         }
         // epilogue: TMEM lane = batch row, column = weight row.  Warp w may read lanes 32*(w%4)..+31.
         if (mbar_wait(d_full, 0, p.status)) {
+            if (threadIdx.x == 32 * kFirstDequantWarp) GEMM_TRACE(3, 0, 0);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int quarter = warp & 3, colq = (warp - kFirstDequantWarp) >> 2;  // 16 warps: 4 lane quarters x 4 column quarters
             const int64_t row = m0 + quarter * 32 + lane;
@@ -382,12 +426,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p
                 if (row < p.m) {
                     const int64_t nbase = (int64_t)blockIdx.x * BN + col0;
                     float *dst = p.y + row * p.y_ld + nbase;
+                    const bool vec = nbase + 32 <= p.n && (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
+                    if (vec) {  // 16-byte stores: a lane owns 32 consecutive outputs of one row
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        if (nbase + j < p.n) {
-                            float f = __uint_as_float(v[j]);
-                            if (p.bias != nullptr) f += __ldg(p.bias + nbase + j);
-                            dst[j] = apply_activation(p.act, f);
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 o;
+                            float *of = reinterpret_cast<float *>(&o);
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                float f = __uint_as_float(v[j + e]);
+                                if (p.bias != nullptr) f += __ldg(p.bias + nbase + j + e);
+                                of[e] = apply_activation(p.act, f);
+                            }
+                            *reinterpret_cast<float4 *>(dst + j) = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            if (nbase + j < p.n) {
+                                float f = __uint_as_float(v[j]);
+                                if (p.bias != nullptr) f += __ldg(p.bias + nbase + j);
+                                dst[j] = apply_activation(p.act, f);
+                            }
                         }
                     }
                 }
@@ -396,6 +456,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    GEMM_TRACE(3, 0, 1);
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(BN) : "memory");
     }
@@ -457,6 +518,14 @@ int launch_gemm_t(const Weight &w, const __nv_bfloat16 *x, int64_t m, const floa
 }
 
 }  // namespace
+
+#ifdef B200Q_TRACE
+}  // namespace b200q
+extern "C" int b200q_debug_set_gemm_trace(unsigned long long *dev_buf) {
+    return cudaMemcpyToSymbol(b200q::g_gemm_trace, &dev_buf, sizeof(dev_buf)) == cudaSuccess ? 0 : -3;
+}
+namespace b200q {
+#endif
 
 int launch_gemm(const Weight &w, const void *x, int x_dtype, int64_t m, const float *bias, int act, float *y,
                 int64_t y_ld, cudaStream_t s) {
