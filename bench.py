@@ -229,10 +229,19 @@ def run_cuda(args) -> None:
                     peer_layers[li][pi](x_dev[k], None, act_types[act])
                     if name in sync_after:
                         bufs.barrier()
+                elif gather == "nccl":
+                    g.backend_fused_quantized_dense(x_dev[k], weights[li][pi], None, quant[t], acts[act], out=y_loc[li][pi])
+                    dist.all_gather_into_tensor(y_full[li][pi], y_loc[li][pi])
+                elif args.fuse_shared_input and name in ("q", "gate"):
+                    # q+k and gate+up read the same activations and share format and K: one launch each
+                    pj = pi + (1 if name == "q" else 1)
+                    g.backend_fused_quantized_dense_batch(
+                        x_dev[k], [weights[li][pi], weights[li][pj]], None, quant[t],
+                        [acts[act], acts[PROJECTIONS[pj][4]]], outs=[y_loc[li][pi], y_loc[li][pj]])
+                elif args.fuse_shared_input and name in ("k", "up"):
+                    pass  # computed together with q / gate
                 else:
                     g.backend_fused_quantized_dense(x_dev[k], weights[li][pi], None, quant[t], acts[act], out=y_loc[li][pi])
-                    if gather == "nccl":
-                        dist.all_gather_into_tensor(y_full[li][pi], y_loc[li][pi])
 
     def select(pred):
         def run():
@@ -332,12 +341,13 @@ def run_cuda(args) -> None:
                                                                    "4 device barriers per layer"}[gather],
                    "inputs": "fixed N(0,1) activations per projection (outputs not chained)",
                    "l2": f"no flush: {local_bytes / 1e6:.0f} MB of weights per GPU per step exceed the 126 MB L2",
-                   "launch": "one CUDA graph of 224 GEMV launches per step"},
+                   "launch": ("one CUDA graph per step; q+k and gate+up of a layer share one launch each (160 launches)"
+                              if (world == 1 and args.fuse_shared_input) else "one CUDA graph of 224 GEMV launches per step")},
         "roofline": roofline,
         "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": int(sum(v.numel() * 4 for v in x_host.values())),
                 "d2h_bytes_per_step": int(y_host.numel() * 4)},
-        "gpu_launches": int(args.steps * LAYERS * len(PROJECTIONS)),
+        "gpu_launches": int(args.steps * LAYERS * (5 if (world == 1 and args.fuse_shared_input) else len(PROJECTIONS))),
         "clocks": clk,
     }
     if rank == 0:
@@ -370,6 +380,8 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--fuse-shared-input", type=int, default=1,
+                    help="1: q+k and gate+up (same activations, format and K) run as one launch each")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"], help="N > 1: how outputs are all-gathered")
     ap.add_argument("--traffic", type=float, default=None, help="dram bytes per launch of the dominant kernel (ncu)")
     args = ap.parse_args()

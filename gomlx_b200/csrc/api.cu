@@ -6,6 +6,7 @@
 #include <memory>
 #include <mutex>
 #include <unordered_map>
+#include <vector>
 
 namespace b200q {
 
@@ -223,6 +224,41 @@ int b200q_dense(b200q_weight_t h, const void *x_dev, int x_dtype, int64_t m, con
     }
     g_last_kernel = B200Q_KERNEL_GEMM_TCGEN05;
     return launch_gemm(*w, x_dev, x_dtype, m, bias_dev, activation, y_dev, y_ld, s);
+}
+
+int b200q_dense_batch(int count, const b200q_weight_t *hs, const void *x_dev, int x_dtype, int64_t m,
+                      const float *const *biases_dev, const int *activations, float *const *ys_dev, const int64_t *y_lds,
+                      void *stream) {
+    if (count < 1 || !hs || !ys_dev || !activations) return fail(B200Q_EINVAL, "dense_batch: bad arguments");
+    if (m == 0) return B200Q_OK;
+    if (!x_dev) return fail(B200Q_EINVAL, "dense_batch: null x");
+    if (x_dtype != B200Q_F32 && x_dtype != B200Q_BF16) return fail(B200Q_EINVAL, "dense_batch: x dtype must be f32 or bf16");
+    if (reinterpret_cast<uintptr_t>(x_dev) & 15) return fail(B200Q_EINVAL, "dense_batch: x must be 16-byte aligned");
+    std::vector<std::shared_ptr<Weight>> ws((size_t)count);
+    bool same = count <= 4 && m <= 16;
+    for (int i = 0; i < count; i++) {
+        ws[i] = find(hs[i]);
+        if (!ws[i]) return fail(B200Q_EHANDLE, "dense_batch: unknown handle");
+        if (!ys_dev[i]) return fail(B200Q_EINVAL, "dense_batch: null y");
+        if (activations[i] < B200Q_ACT_NONE || activations[i] > B200Q_ACT_TANH) return fail(B200Q_EINVAL, "dense_batch: bad activation");
+        if (y_lds && y_lds[i] != 0 && y_lds[i] < ws[i]->n) return fail(B200Q_EINVAL, "dense_batch: y_ld smaller than N");
+        same = same && ws[i]->type == ws[0]->type && ws[i]->k == ws[0]->k && ws[i]->device == ws[0]->device;
+    }
+    if (!same) {  // different formats / K, or not a decode shape: one launch per matrix, same results
+        for (int i = 0; i < count; i++) {
+            int rc = b200q_dense(hs[i], x_dev, x_dtype, m, biases_dev ? biases_dev[i] : nullptr, activations[i], ys_dev[i],
+                                 y_lds ? y_lds[i] : 0, stream);
+            if (rc != 0) return rc;
+        }
+        return B200Q_OK;
+    }
+    B200Q_CUDA(cudaSetDevice(ws[0]->device));
+    const Weight *wp[4];
+    int64_t lds[4];
+    for (int i = 0; i < count; i++) wp[i] = ws[i].get(), lds[i] = (y_lds && y_lds[i]) ? y_lds[i] : ws[i]->n;
+    g_last_kernel = B200Q_KERNEL_GEMV_MMA;
+    return launch_gemv_batch(count, wp, x_dev, x_dtype, (int)m, biases_dev, activations, ys_dev, lds,
+                             static_cast<cudaStream_t>(stream));
 }
 
 int b200q_dense_scatter(b200q_weight_t h, const void *x_dev, int x_dtype, int64_t m, const float *bias_dev, int activation,

@@ -54,18 +54,30 @@ namespace cg = cooperative_groups;
 namespace b200q {
 namespace {
 
-struct GemvParams {
+// One weight matrix of a launch.  A launch may cover up to kMaxSegments matrices of the same format
+// and K that read the same activations (q and k, gate and up): their row tiles are simply numbered
+// through, so the scheduler sees one tall matrix and the fixed cost of a launch is paid once.
+constexpr int kMaxSegments = 4;
+struct Segment {
     const uint8_t *tiles;
-    const void *x;
     const float *bias;
     float *y;
+    int64_t n, y_ld;
+    int rt0;  // first row tile of this matrix in the launch-wide numbering
+    int act;
+};
+
+struct GemvParams {
+    Segment seg[kMaxSegments];
+    int nseg;
+    const void *x;
     float *y_peer[7];  // the same output buffer on the other GPUs of a row-sharded layer (NVLink peer memory)
     int npeers;        // number of valid entries in y_peer
     int *status;
-    int64_t n, k, y_ld;
+    int64_t k;
     int64_t row_off;   // first output column of this shard inside the full [m, N_total] result
     int64_t rt, kt;  // row tiles (16 rows) and k tiles (256 values) of the weight
-    int m, x_dtype, act;
+    int m, x_dtype;
     int splits;     // CTAs per cluster (power of two); split s owns k tiles [s*kts, (s+1)*kts)
     int split_shift;
     int kts;
@@ -580,6 +592,14 @@ __device__ __forceinline__ void stage_x(const GemvParams &p, int64_t k0, int kc,
     }
 }
 
+// Matrix that launch-wide row tile `rt` belongs to.
+__device__ __forceinline__ int segment_of(const GemvParams &p, int rt) {
+    int s = 0;
+#pragma unroll
+    for (int i = 1; i < kMaxSegments; i++) s += (i < p.nseg && rt >= p.seg[i].rt0) ? 1 : 0;
+    return s;
+}
+
 // Grid = nclusters x splits CTAs; the `splits` CTAs of a cluster hold the K slices of the same rows.
 // Inside a CTA the work is cut into units = (row tile, k part); warp w takes units w, w + nwarps, ...
 // and streams each unit's tiles through its private ring of shared-memory slots.
@@ -644,7 +664,8 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
     producer_skip_empty();
     auto issue_next = [&]() {
         const int nt = min(p.tps, pk1 - pk);
-        const uint8_t *src = p.tiles + ((int64_t)(r0 + prow) * p.kt + pk) * (int64_t)F::TILE;
+        const Segment &sg = p.seg[segment_of(p, r0 + prow)];
+        const uint8_t *src = sg.tiles + ((int64_t)(r0 + prow - sg.rt0) * p.kt + pk) * (int64_t)F::TILE;
         mbar_expect_tx(bars_s + 8 * pd, nt * F::TILE);
         bulk_load(ring_s + pd * slot_bytes, src, nt * F::TILE, bars_s + 8 * pd);
         if (++pd == p.depth) pd = 0;
@@ -753,9 +774,10 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
     const int e_end = min((split + 1) * per, total_e);
     for (int e = split * per + (int)threadIdx.x; e < e_end; e += blockDim.x) {
         const int ln = e & 31, i = (e >> 5) & 3, nb = (e >> 7) % NB, ri = (e >> 7) / NB;
-        const int64_t row = (int64_t)(r0 + ri) * 16 + (ln >> 2) + 8 * (i >> 1);
+        const Segment &sg = p.seg[segment_of(p, r0 + ri)];
+        const int64_t row = (int64_t)(r0 + ri - sg.rt0) * 16 + (ln >> 2) + 8 * (i >> 1);
         const int col = 8 * nb + 2 * (ln & 3) + (i & 1);
-        if (row < p.n && col < p.m) {
+        if (row < sg.n && col < p.m) {
             float v = 0.0f;
             const int within = (e & 127) + nb * 128;  // offset inside a unit's block
             for (int r = 0; r < p.splits; r++) {
@@ -767,13 +789,13 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
                     v += base[(size_t)(ri * p.kp + q) * NB * 128 + within];
                 }
             }
-            if (p.bias != nullptr) v += __ldg(p.bias + row);
+            if (sg.bias != nullptr) v += __ldg(sg.bias + row);
             // The finished value goes to this GPU's buffer and, for a row-sharded layer, straight into the
             // buffer of every peer GPU (plain stores over NVLink): the all-gather of the outputs happens
             // in the epilogue, tile by tile, instead of in a collective after the kernel.
-            const float out = apply_activation(p.act, v);
-            const int64_t at = (int64_t)col * p.y_ld + p.row_off + row;
-            p.y[at] = out;
+            const float out = apply_activation(sg.act, v);
+            const int64_t at = (int64_t)col * sg.y_ld + p.row_off + row;
+            sg.y[at] = out;
             for (int pr = 0; pr < p.npeers; pr++) p.y_peer[pr][at] = out;
         }
     }
@@ -924,29 +946,49 @@ int launch_nb(const Weight &w, const GemvParams &p, cudaStream_t s) {
 
 }  // namespace
 
-int launch_gemv(const Weight &w, const void *x, int x_dtype, int m, const float *bias, int act, float *y, int64_t y_ld,
-                cudaStream_t s, float *const *y_peers, int npeers, int64_t row_off) {
+int launch_gemv_batch(int count, const Weight *const *ws, const void *x, int x_dtype, int m, const float *const *biases,
+                      const int *acts, float *const *ys, const int64_t *y_lds, cudaStream_t s, float *const *y_peers,
+                      int npeers, int64_t row_off) {
     if (m < 1 || m > 16) return fail(B200Q_EINVAL, "gemv: m must be in 1..16");
-    if (npeers < 0 || npeers > 7 || (npeers > 0 && y_peers == nullptr)) return fail(B200Q_EINVAL, "gemv: bad peer list");
+    if (count < 1 || count > kMaxSegments) return fail(B200Q_EINVAL, "gemv: 1..4 matrices per launch");
+    if (npeers < 0 || npeers > 7 || (npeers > 0 && (y_peers == nullptr || count != 1)))
+        return fail(B200Q_EINVAL, "gemv: bad peer list");
     GemvParams p{};
-    p.tiles = w.tiles;
+    Weight all = *ws[0];  // launch-wide view: same format, K and device, row tiles numbered through
+    int64_t rt = 0;
+    for (int i = 0; i < count; i++) {
+        const Weight &w = *ws[i];
+        if (w.type != all.type || w.k != all.k || w.device != all.device)
+            return fail(B200Q_EINVAL, "gemv: batched matrices must share format, K and device");
+        p.seg[i].tiles = w.tiles, p.seg[i].bias = biases ? biases[i] : nullptr, p.seg[i].y = ys[i];
+        p.seg[i].n = w.n, p.seg[i].y_ld = y_lds[i], p.seg[i].rt0 = (int)rt, p.seg[i].act = acts[i];
+        rt += w.rt;
+    }
+    p.nseg = count;
+    all.rt = rt;
     p.x = x;
-    p.bias = bias;
-    p.y = y;
     for (int i = 0; i < npeers; i++) p.y_peer[i] = y_peers[i];
     p.npeers = npeers;
     p.row_off = row_off;
-    p.n = w.n, p.k = w.k, p.y_ld = y_ld;
-    p.rt = w.rt, p.kt = w.kt;
-    p.m = m, p.x_dtype = x_dtype, p.act = act;
-    p.status = w.status;
-    switch (w.type) {
-    case kQ4_0: return launch_nb<kQ4_0>(w, p, s);
-    case kQ8_0: return launch_nb<kQ8_0>(w, p, s);
-    case kQ4_K: return launch_nb<kQ4_K>(w, p, s);
-    case kQ6_K: return launch_nb<kQ6_K>(w, p, s);
+    p.k = all.k;
+    p.rt = all.rt, p.kt = all.kt;
+    p.m = m, p.x_dtype = x_dtype;
+    p.status = all.status;
+    switch (all.type) {
+    case kQ4_0: return launch_nb<kQ4_0>(all, p, s);
+    case kQ8_0: return launch_nb<kQ8_0>(all, p, s);
+    case kQ4_K: return launch_nb<kQ4_K>(all, p, s);
+    case kQ6_K: return launch_nb<kQ6_K>(all, p, s);
     }
     return fail(B200Q_ENOTIMPL, "gemv: unsupported GGML type");
+}
+
+int launch_gemv(const Weight &w, const void *x, int x_dtype, int m, const float *bias, int act, float *y, int64_t y_ld,
+                cudaStream_t s, float *const *y_peers, int npeers, int64_t row_off) {
+    const Weight *ws[1] = {&w};
+    const float *biases[1] = {bias};
+    float *ys[1] = {y};
+    return launch_gemv_batch(1, ws, x, x_dtype, m, biases, &act, ys, &y_ld, s, y_peers, npeers, row_off);
 }
 
 }  // namespace b200q

@@ -215,6 +215,34 @@ def backend_fused_quantized_dense(x, weights, bias, wq: Quantization,
     return y.reshape(*x.shape[:-1], w.n)
 
 
+def backend_fused_quantized_dense_batch(x, weights, biases, wq: Quantization, activations, outs=None):
+    """Several BackendFusedQuantizedDense nodes on the same activations (q/k/v, gate/up) as one launch
+    (``b200q_dense_batch``).  ``weights``: ResidentWeight list; ``biases``: list with None entries or None;
+    ``activations``: one ActivationType per weight.  Returns the list of ``[m, N_i]`` float32 outputs."""
+    _check_ggml(wq, "BackendFusedQuantizedDense")
+    if not (torch is not None and isinstance(x, torch.Tensor) and x.is_cuda):
+        raise ValueError("the batched form takes CUDA activations")
+    dev = x.device.index
+    ws = [resident(w, wq, dev) for w in weights]
+    k = ws[0].k
+    x2 = x.reshape(-1, k).contiguous()
+    m = x2.shape[0]
+    count = len(ws)
+    if outs is None:
+        outs = [torch.empty((m, w.n), device=x.device, dtype=torch.float32) for w in ws]
+    bs = [None] * count if biases is None else [None if b is None else b.to(device=x.device, dtype=torch.float32).contiguous()
+                                                for b in biases]
+    handles = (ctypes.c_uint64 * count)(*[w.handle for w in ws])
+    bias_arr = (ctypes.c_void_p * count)(*[None if b is None else b.data_ptr() for b in bs])
+    act_arr = (ctypes.c_int * count)(*[int(a) for a in activations])
+    y_arr = (ctypes.c_void_p * count)(*[y.data_ptr() for y in outs])
+    ld_arr = (ctypes.c_int64 * count)(*[y.stride(0) if m > 0 else 0 for y in outs])
+    nat.check(nat.lib().b200q_dense_batch(count, handles, ctypes.c_void_p(x2.data_ptr()),
+                                          nat.F32 if x.dtype == torch.float32 else nat.BF16, m, bias_arr, act_arr, y_arr,
+                                          ld_arr, _stream_ptr(dev)))
+    return outs
+
+
 def quantized_dense(x, weights, quant: Quantization, bias=None, *optional_activation: Activation):
     """nn.QuantizedDense (ml/nn/quantized_dense.go:31-71).  At most one activation may be given;
     it is translated with ``to_backend`` so types the fused op cannot apply are dropped, as in the

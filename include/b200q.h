@@ -123,6 +123,15 @@ int b200q_dequantize(b200q_weight_t w, float *out_dev, void *stream);
 int b200q_dense(b200q_weight_t w, const void *x_dev, int x_dtype, int64_t m, const float *bias_dev, int activation,
                 float *y_dev, int64_t y_ld, void *stream);
 
+/* Several FusedQuantizedDense nodes that read the same activations (q/k/v, gate/up of a decoder layer:
+ * ml/zoo/transformer/transformer.go:909-924,1286-1294 issue them one after another on the same x), run
+ * as one launch when they share format, K and device and m <= 16; otherwise one launch each.  Results are
+ * identical to `count` calls of b200q_dense.  biases_dev may be NULL or hold NULL entries; y_lds may be
+ * NULL (dense outputs). */
+int b200q_dense_batch(int count, const b200q_weight_t *ws, const void *x_dev, int x_dtype, int64_t m,
+                      const float *const *biases_dev, const int *activations, float *const *ys_dev, const int64_t *y_lds,
+                      void *stream);
+
 /* Row-sharded decode (m <= 16) with the all-gather of the outputs fused into the kernel.  The
  * reference's graph layer has no all-gather (only AllReduce, core/graph/distributed.go:217-248); this
  * is the multi-GPU form of b200q_dense for a weight uploaded as a row shard.  `w` holds rows

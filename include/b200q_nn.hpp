@@ -1,0 +1,239 @@
+// C++ host-side mirror of the GoMLX quantized dense / gather API over the b200q C ABI.
+//
+// The reference's host language is Go; where no Go toolchain is available this header is the
+// compiled host layer: same names, argument meaning and error behaviour as
+//
+//   graph.Quantization                      core/graph/fused_ops.go:18-48
+//   graph.BackendFusedQuantizedDense        core/graph/fused_ops.go:195-245
+//   graph.BackendQuantizedEmbeddingLookup   core/graph/fused_ops.go:281-309
+//   nn.QuantizedDense                       ml/nn/quantized_dense.go:31-71
+//   nn.QuantizedGather                      ml/nn/quantized_gather.go:30-43
+//   ggml.CanDecompose                       ml/ggml/dequant.go:20-27
+//   activation.Type.ToBackend               ml/layers/activation/activation.go:58-75
+//   tensors: upload once / Finalize         core/tensors/ondevice.go:59-71,130-144,285-295
+//
+// Go panics become C++ exceptions: b200q::Error for failures, b200q::NotImplemented where Go code
+// would see compute.IsNotImplemented(err) and fall back to the decomposed graph.
+// Header-only; link with -lb200q.  All arithmetic happens in the library, on the GPU.
+#pragma once
+
+#include <cstdint>
+#include <initializer_list>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "b200q.h"
+
+namespace b200q {
+
+struct Error : std::runtime_error {
+    int code;
+    Error(int c, const std::string &m) : std::runtime_error("b200q: " + m), code(c) {}
+};
+struct NotImplemented : Error {  // compute.ErrNotImplemented
+    explicit NotImplemented(const std::string &m) : Error(B200Q_ENOTIMPL, m) {}
+};
+inline void check(int rc) {
+    if (rc >= 0) return;
+    const std::string msg = b200q_last_error();
+    if (rc == B200Q_ENOTIMPL) throw NotImplemented(msg);
+    throw Error(rc, msg);
+}
+
+enum class QuantizationScheme { QuantLinear, QuantNF4, QuantGGML };  // compute.QuantizationScheme
+
+enum class GGMLQuantType : int { GGMLQ4_0 = 2, GGMLQ8_0 = 8, GGMLQ4_K = 12, GGMLQ6_K = 14, GGMLIQ4NL = 20 };
+inline int BytesPerBlock(GGMLQuantType t) { return b200q_ggml_bytes_per_block(static_cast<int>(t)); }
+inline int ValuesPerBlock(GGMLQuantType t) { return b200q_ggml_values_per_block(static_cast<int>(t)); }
+inline std::string String(GGMLQuantType t) {
+    const char *s = b200q_ggml_type_name(static_cast<int>(t));
+    return s ? s : "unknown";
+}
+
+enum class ActivationType { ActivationNone, ActivationGelu, ActivationRelu, ActivationSilu, ActivationHardSwish, ActivationTanh };
+
+namespace activation {
+enum class Type {
+    TypeNone, TypeRelu, TypeLeakyRelu, TypeSigmoid, TypeHardSigmoid, TypeTanh, TypeSwish, TypeSilu, TypeHardSwish,
+    TypeSelu, TypeGelu, TypeGeluApprox, TypeSwiGLU
+};
+// Types the fused op cannot apply map to ActivationNone without an error, as in the reference.
+inline ActivationType ToBackend(Type t) {
+    switch (t) {
+    case Type::TypeGelu:
+    case Type::TypeGeluApprox: return ActivationType::ActivationGelu;
+    case Type::TypeRelu: return ActivationType::ActivationRelu;
+    case Type::TypeSwish:
+    case Type::TypeSilu: return ActivationType::ActivationSilu;
+    case Type::TypeHardSwish: return ActivationType::ActivationHardSwish;
+    case Type::TypeTanh: return ActivationType::ActivationTanh;
+    default: return ActivationType::ActivationNone;
+    }
+}
+}  // namespace activation
+
+namespace ggml {
+inline bool CanDecompose(GGMLQuantType t) { return b200q_ggml_can_decompose(static_cast<int>(t)) != 0; }
+}  // namespace ggml
+
+// A float32 / int32 array on one device (Backend.BufferFromFlatData, Buffer.ToFlatData, Buffer.Finalize).
+template <class T>
+class Buffer {
+  public:
+    Buffer(int device, std::vector<int64_t> shape) : device_(device), shape_(std::move(shape)) {
+        check(b200q_buffer_alloc(device_, bytes(), &ptr_));
+    }
+    Buffer(int device, std::vector<int64_t> shape, const std::vector<T> &flat) : Buffer(device, std::move(shape)) {
+        if ((int64_t)flat.size() != size()) throw Error(B200Q_EINVAL, "BufferFromFlatData: size does not match shape");
+        if (!flat.empty()) {
+            check(b200q_buffer_h2d(device_, ptr_, flat.data(), bytes(), nullptr));
+            check(b200q_stream_sync(device_, nullptr));
+        }
+    }
+    Buffer(const Buffer &) = delete;
+    Buffer &operator=(const Buffer &) = delete;
+    Buffer(Buffer &&o) noexcept : device_(o.device_), shape_(std::move(o.shape_)), ptr_(o.ptr_) { o.ptr_ = nullptr; }
+    ~Buffer() { Finalize(); }
+    void Finalize() {
+        if (ptr_) b200q_buffer_free(device_, ptr_);
+        ptr_ = nullptr;
+    }
+    std::vector<T> ToFlatData() const {
+        std::vector<T> out((size_t)size());
+        if (!out.empty()) {
+            check(b200q_buffer_d2h(device_, out.data(), ptr_, bytes(), nullptr));
+            check(b200q_stream_sync(device_, nullptr));
+        }
+        return out;
+    }
+    int64_t size() const {
+        int64_t n = 1;
+        for (auto d : shape_) n *= d;
+        return n;
+    }
+    size_t bytes() const { return (size_t)size() * sizeof(T); }
+    const std::vector<int64_t> &shape() const { return shape_; }
+    T *data() const { return static_cast<T *>(ptr_); }
+    int device() const { return device_; }
+
+  private:
+    int device_;
+    std::vector<int64_t> shape_;
+    void *ptr_ = nullptr;
+};
+
+// Packed GGML weights [N, bytesPerRow] uint8 resident on one device: uploaded once, reused by every
+// call, released by Finalize() or destruction (never donated).
+class Weights {
+  public:
+    Weights(int device, GGMLQuantType type, const std::vector<std::vector<uint8_t>> &rows) : type_(type) {
+        if (rows.empty()) throw Error(B200Q_EINVAL, "weights must have at least one row");
+        const size_t bpr = rows[0].size();
+        std::vector<uint8_t> flat;
+        flat.reserve(rows.size() * bpr);
+        for (auto &r : rows) {
+            if (r.size() != bpr) throw Error(B200Q_EINVAL, "ragged weight rows");
+            flat.insert(flat.end(), r.begin(), r.end());
+        }
+        init(device, (int64_t)rows.size(), (int64_t)bpr, flat.data());
+    }
+    Weights(int device, GGMLQuantType type, int64_t n, int64_t bytes_per_row, const uint8_t *bytes) : type_(type) {
+        init(device, n, bytes_per_row, bytes);
+    }
+    Weights(const Weights &) = delete;
+    Weights &operator=(const Weights &) = delete;
+    ~Weights() { Finalize(); }
+    void Finalize() {
+        if (h_) b200q_weight_free(h_);
+        h_ = 0;
+    }
+    b200q_weight_t handle() const { return h_; }
+    GGMLQuantType type() const { return type_; }
+    int64_t N() const { return n_; }
+    int64_t K() const { return k_; }
+    int device() const { return device_; }
+
+  private:
+    void init(int device, int64_t n, int64_t bpr, const uint8_t *bytes) {
+        const int bpb = BytesPerBlock(type_), vpb = ValuesPerBlock(type_);
+        if (bpb == 0) throw NotImplemented("unknown GGML type");
+        if (bpr % bpb) throw Error(B200Q_EINVAL, "bytesPerRow is not a multiple of the block size");
+        device_ = device, n_ = n, k_ = bpr / bpb * vpb;
+        check(b200q_weight_upload(device, static_cast<int>(type_), n_, k_, bytes, n * bpr, 0, &h_));
+    }
+    GGMLQuantType type_;
+    int device_ = 0;
+    int64_t n_ = 0, k_ = 0;
+    b200q_weight_t h_ = 0;
+};
+
+// graph.Quantization.  For QuantGGML only Scheme and GGMLType are used (scales live in the blocks).
+struct Quantization {
+    QuantizationScheme Scheme = QuantizationScheme::QuantGGML;
+    GGMLQuantType GGMLType = GGMLQuantType::GGMLQ8_0;
+    const Buffer<float> *Scale = nullptr;
+    const Buffer<float> *ZeroPoint = nullptr;
+    int BlockAxis = 0;
+    int BlockSize = 0;
+};
+
+namespace graph {
+
+// BackendFusedQuantizedDense: act(x @ dequant(weights)^T + bias); x [batch..., K] f32, result [batch..., N].
+inline Buffer<float> BackendFusedQuantizedDense(const Buffer<float> &x, const Weights &weights, const Buffer<float> *bias,
+                                                const Quantization *wq, ActivationType act) {
+    if (wq == nullptr) throw Error(B200Q_EINVAL, "BackendFusedQuantizedDense: wq must not be nil");
+    if (wq->Scale == nullptr && wq->Scheme != QuantizationScheme::QuantGGML)
+        throw Error(B200Q_EINVAL, "BackendFusedQuantizedDense: wq.Scale must not be nil for this scheme");
+    if (wq->Scheme != QuantizationScheme::QuantGGML)
+        throw NotImplemented("BackendFusedQuantizedDense: only the QuantGGML scheme runs on this backend");
+    if (x.shape().empty() || x.shape().back() != weights.K())
+        throw Error(B200Q_EINVAL, "QuantizedDense expects x shaped [batch..., K] matching the weights' K");
+    if (bias && bias->size() != weights.N()) throw Error(B200Q_EINVAL, "bias must be shaped [N]");
+    std::vector<int64_t> out_shape = x.shape();
+    out_shape.back() = weights.N();
+    const int64_t m = x.size() / weights.K();
+    Buffer<float> y(x.device(), out_shape);
+    check(b200q_dense(weights.handle(), x.data(), B200Q_F32, m, bias ? bias->data() : nullptr, static_cast<int>(act),
+                      y.data(), 0, nullptr));
+    check(b200q_weight_check(weights.handle(), nullptr));
+    return y;
+}
+
+// BackendQuantizedEmbeddingLookup: indices [batch..., 1] int32 -> [batch..., K] f32.
+inline Buffer<float> BackendQuantizedEmbeddingLookup(const Weights &data, const Buffer<int32_t> &indices, const Quantization *tq) {
+    if (tq == nullptr) throw Error(B200Q_EINVAL, "BackendQuantizedEmbeddingLookup: tq must not be nil");
+    if (indices.shape().empty() || indices.shape().back() != 1)
+        throw Error(B200Q_EINVAL, "indices must have last dimension 1");
+    std::vector<int64_t> out_shape = indices.shape();
+    out_shape.back() = data.K();
+    Buffer<float> out(indices.device(), out_shape);
+    check(b200q_embedding_lookup(data.handle(), indices.data(), indices.size(), out.data(), nullptr));
+    return out;
+}
+
+}  // namespace graph
+
+namespace nn {
+
+// nn.QuantizedDense: at most one activation; it is translated with ToBackend first.
+inline Buffer<float> QuantizedDense(const Buffer<float> &x, const Weights &weights, const Quantization *quant,
+                                    const Buffer<float> *bias, std::initializer_list<activation::Type> optionalActivation = {}) {
+    if (optionalActivation.size() > 1)
+        throw Error(B200Q_EINVAL, "nn.QuantizedDense() can only take one optional activation");
+    const activation::Type act = optionalActivation.size() ? *optionalActivation.begin() : activation::Type::TypeNone;
+    return graph::BackendFusedQuantizedDense(x, weights, bias, quant, activation::ToBackend(act));
+}
+
+// nn.QuantizedGather: only the QuantGGML scheme is supported.
+inline Buffer<float> QuantizedGather(const Weights &table, const Buffer<int32_t> &indices, const Quantization *quant) {
+    if (quant == nullptr || quant->Scheme != QuantizationScheme::QuantGGML)
+        throw Error(B200Q_EINVAL, "nn.QuantizedGather: only QuantGGML scheme is supported");
+    return graph::BackendQuantizedEmbeddingLookup(table, indices, quant);
+}
+
+}  // namespace nn
+}  // namespace b200q

@@ -1,0 +1,141 @@
+// C++ host-layer tests that read like the reference's own (gomlx/gomlx):
+//   ml/nn/quantized_dense_test.go:272-401   TestQuantizedDense_GGML_Q8_0 / _Q4_0
+//   ml/nn/quantized_gather_test.go:17-121   TestQuantizedGather_GGML_Q8_0 / _Q4_0
+// Every case runs twice, as graphtest.RunTestGraphFnWithBackend does (core/graph/graphtest/graphtest.go:54-107),
+// and compares with an absolute delta.  Needs a GPU; exits non-zero on the first failure.
+#include <cmath>
+#include <cstdio>
+#include <functional>
+
+#include "b200q_nn.hpp"
+
+using namespace b200q;
+using Rows = std::vector<std::vector<uint8_t>>;
+
+static int failures = 0;
+
+static void RunTestGraphFn(const char *test, const char *name, const std::function<Buffer<float>()> &graphFn,
+                           const std::vector<float> &want, double delta) {
+    for (int run = 0; run < 2; run++) {
+        std::vector<float> got;
+        try {
+            got = graphFn().ToFlatData();
+        } catch (const std::exception &e) {
+            std::printf("FAIL %s/%s: %s\n", test, name, e.what());
+            failures++;
+            return;
+        }
+        bool ok = got.size() == want.size();
+        for (size_t i = 0; ok && i < want.size(); i++) ok = std::fabs(got[i] - want[i]) <= delta;
+        if (!ok) {
+            std::printf("FAIL %s/%s (run %d)\n", test, name, run);
+            failures++;
+            return;
+        }
+    }
+    std::printf("ok   %s/%s\n", test, name);
+}
+
+static std::vector<uint8_t> q8Row(uint8_t scaleHi, std::initializer_list<int> ones) {
+    std::vector<uint8_t> row(34, 0);
+    row[0] = 0x00, row[1] = scaleHi;  // fp16 little endian
+    for (int i : ones) row[2 + i] = 1;
+    return row;
+}
+static std::vector<uint8_t> q4Row(uint8_t scaleHi, int nineAt) {
+    std::vector<uint8_t> row(18, 0x88);  // nibble 8 -> (8-8) = 0
+    row[0] = 0x00, row[1] = scaleHi;
+    row[2 + nineAt] = 0x89;  // low nibble 9 -> +1*scale, high nibble 8 -> 0
+    return row;
+}
+
+int main() {
+    int ndev = 0;
+    if (b200q_device_count(&ndev) != B200Q_OK || ndev < 1) {
+        std::printf("no CUDA device: %s\n", b200q_last_error());
+        return 2;
+    }
+    std::vector<float> xData(32, 0.f);
+    xData[0] = xData[1] = 1.f;
+
+    {  // TestQuantizedDense_GGML_Q8_0
+        Weights w(0, GGMLQuantType::GGMLQ8_0, Rows{q8Row(0x40, {0}), q8Row(0x42, {1})});
+        Quantization quant{QuantizationScheme::QuantGGML, GGMLQuantType::GGMLQ8_0};
+        RunTestGraphFn("TestQuantizedDense_GGML_Q8_0", "basic", [&] {
+            Buffer<float> x(0, {1, 32}, xData);
+            return nn::QuantizedDense(x, w, &quant, nullptr);
+        }, {2.0f, 3.0f}, 1e-4);
+        RunTestGraphFn("TestQuantizedDense_GGML_Q8_0", "with_bias", [&] {
+            Buffer<float> x(0, {1, 32}, xData), b(0, {2}, {0.5f, -0.5f});
+            return nn::QuantizedDense(x, w, &quant, &b);
+        }, {2.5f, 2.5f}, 1e-4);
+        RunTestGraphFn("TestQuantizedDense_GGML_Q8_0", "batch", [&] {
+            std::vector<float> two(xData);
+            two.resize(64, 0.f);
+            two[32] = 0.5f;
+            Buffer<float> x(0, {2, 32}, two);
+            return nn::QuantizedDense(x, w, &quant, nullptr);
+        }, {2.0f, 3.0f, 1.0f, 0.0f}, 1e-4);
+    }
+    {  // TestQuantizedDense_GGML_Q4_0
+        Weights w(0, GGMLQuantType::GGMLQ4_0, Rows{q4Row(0x40, 0), q4Row(0x42, 1)});
+        Quantization quant{QuantizationScheme::QuantGGML, GGMLQuantType::GGMLQ4_0};
+        RunTestGraphFn("TestQuantizedDense_GGML_Q4_0", "basic", [&] {
+            Buffer<float> x(0, {1, 32}, xData);
+            return nn::QuantizedDense(x, w, &quant, nullptr);
+        }, {2.0f, 3.0f}, 1e-4);
+        RunTestGraphFn("TestQuantizedDense_GGML_Q4_0", "with_silu", [&] {
+            Buffer<float> x(0, {1, 32}, xData);
+            return nn::QuantizedDense(x, w, &quant, nullptr, {activation::Type::TypeSilu});
+        }, {1.7616f, 2.8577f}, 1e-3);
+    }
+    {  // TestQuantizedGather_GGML_Q8_0
+        Weights table(0, GGMLQuantType::GGMLQ8_0, Rows{q8Row(0x40, {0}), q8Row(0x42, {1}), q8Row(0x3C, {0, 1})});
+        Quantization quant{QuantizationScheme::QuantGGML, GGMLQuantType::GGMLQ8_0};
+        std::vector<float> e(64, 0.f);
+        e[0] = e[1] = 1.0f, e[32] = 2.0f;
+        RunTestGraphFn("TestQuantizedGather_GGML_Q8_0", "basic", [&] {
+            Buffer<int32_t> idx(0, {2, 1}, {2, 0});
+            return nn::QuantizedGather(table, idx, &quant);
+        }, e, 1e-4);
+        std::vector<float> e2(32, 0.f);
+        e2[1] = 3.0f;
+        RunTestGraphFn("TestQuantizedGather_GGML_Q8_0", "single", [&] {
+            Buffer<int32_t> idx(0, {1, 1}, {1});
+            return nn::QuantizedGather(table, idx, &quant);
+        }, e2, 1e-4);
+    }
+    {  // TestQuantizedGather_GGML_Q4_0
+        Weights table(0, GGMLQuantType::GGMLQ4_0, Rows{q4Row(0x40, 0), q4Row(0x42, 1)});
+        Quantization quant{QuantizationScheme::QuantGGML, GGMLQuantType::GGMLQ4_0};
+        std::vector<float> e(64, 0.f);
+        e[1] = 3.0f, e[32] = 2.0f;
+        RunTestGraphFn("TestQuantizedGather_GGML_Q4_0", "basic", [&] {
+            Buffer<int32_t> idx(0, {2, 1}, {1, 0});
+            return nn::QuantizedGather(table, idx, &quant);
+        }, e, 1e-4);
+    }
+    {  // error behaviour at the boundary
+        Quantization lin{QuantizationScheme::QuantLinear};
+        Weights w(0, GGMLQuantType::GGMLQ8_0, Rows{q8Row(0x40, {0})});
+        Buffer<float> x(0, {1, 32}, xData), scale(0, {1}, {1.0f});
+        bool threw = false;
+        try { nn::QuantizedDense(x, w, &lin, nullptr); } catch (const NotImplemented &) {} catch (const Error &) { threw = true; }
+        lin.Scale = &scale;
+        bool notimpl = false;
+        try { nn::QuantizedDense(x, w, &lin, nullptr); } catch (const NotImplemented &) { notimpl = true; }
+        bool two_acts = false;
+        Quantization q{QuantizationScheme::QuantGGML, GGMLQuantType::GGMLQ8_0};
+        try { nn::QuantizedDense(x, w, &q, nullptr, {activation::Type::TypeRelu, activation::Type::TypeTanh}); } catch (const Error &) { two_acts = true; }
+        bool iq4 = false;
+        try { Weights bad(0, GGMLQuantType::GGMLIQ4NL, Rows{std::vector<uint8_t>(18, 0)}); } catch (const NotImplemented &) { iq4 = true; }
+        if (threw && notimpl && two_acts && iq4 && ggml::CanDecompose(GGMLQuantType::GGMLQ4_0) && !ggml::CanDecompose(GGMLQuantType::GGMLQ4_K)) {
+            std::printf("ok   error_behaviour\n");
+        } else {
+            std::printf("FAIL error_behaviour %d %d %d %d\n", threw, notimpl, two_acts, iq4);
+            failures++;
+        }
+    }
+    std::printf(failures ? "FAILED (%d)\n" : "PASS\n", failures);
+    return failures ? 1 : 0;
+}

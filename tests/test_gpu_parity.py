@@ -185,6 +185,37 @@ def test_gemm_prefill_config_shapes(oracle):
         assert np.abs(y[:, rows] - ref).max() <= 1.5 * TOL_GEMM * np.abs(pre).max()
 
 
+@pytest.mark.parametrize("name", ["Q4_K", "Q8_0"])
+@pytest.mark.parametrize("m", [1, 7, 16])
+def test_batched_projections_match_single_launches(oracle, name, m):
+    """q/k- or gate/up-style groups: several matrices on the same x in one launch (b200q_dense_batch)."""
+    t = TYPES[name]
+    k = 1024
+    shapes = [272, 64, 1000]
+    ws = [g.upload(oracle.make_weights(int(t), n, k, seed=n), t) for n in shapes]
+    rng = np.random.default_rng(m)
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda()
+    biases = [torch.randn(shapes[0], device="cuda"), None, torch.randn(shapes[2], device="cuda")]
+    acts = [g.ActivationType.SILU, g.ActivationType.NONE, g.ActivationType.RELU]
+    outs = g.backend_fused_quantized_dense_batch(x, ws, biases, quant(t), acts)
+    for w, b, a, y in zip(ws, biases, acts, outs):
+        want = g.backend_fused_quantized_dense(x, w, b, quant(t), a)
+        assert y.shape == want.shape
+        assert float((y - want).abs().max()) <= 1e-5 * max(1.0, float(want.abs().max()))
+    # mixed formats fall back to one launch per matrix with the same results
+    other = g.upload(oracle.make_weights(14, 48, k, seed=3), g.GGMLQuantType.Q6_K)
+    y2 = torch.empty(m, 48, device="cuda")
+    hs = (ctypes.c_uint64 * 2)(ws[0].handle, other.handle)
+    ya = (ctypes.c_void_p * 2)(outs[0].data_ptr(), y2.data_ptr())
+    aa = (ctypes.c_int * 2)(0, 0)
+    assert nat.lib().b200q_dense_batch(2, hs, ctypes.c_void_p(x.data_ptr()), nat.F32, m, None, aa, ya, None, None) == 0
+    torch.cuda.synchronize()
+    want = g.backend_fused_quantized_dense(x, other, None, quant(g.GGMLQuantType.Q6_K))
+    assert torch.equal(y2, want)
+    for w in ws + [other]:
+        w.free()
+
+
 # ----------------------------------------------------------------------------- BASELINE shapes
 @pytest.mark.parametrize("name,n,k,sigma,ms", [
     ("Q8_0", 4096, 4096, 0.02, [1]),                 # configs[0]
@@ -304,3 +335,13 @@ def test_argument_errors(oracle):
     assert rc == nat.EINVAL and b"aligned" in nat.lib().b200q_last_error()
     rc = nat.lib().b200q_dense(wr.handle, ctypes.c_void_p(x.data_ptr()), 7, 1, None, 0, ctypes.c_void_p(y.data_ptr()), 0, None)
     assert rc == nat.EINVAL
+
+
+# ----------------------------------------------------------------------------- C++ host layer
+def test_cpp_host_layer_reference_cases():
+    """include/b200q_nn.hpp (the compiled host mirror of the Go API) against the reference's test cases."""
+    import subprocess
+    cpp = os.path.join(os.path.dirname(os.path.abspath(__file__)), "cpp")
+    subprocess.check_call(["make", "-C", cpp, "quantized_dense_test"], stdout=subprocess.DEVNULL)
+    out = subprocess.run([os.path.join(cpp, "quantized_dense_test")], capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0 and "PASS" in out.stdout, out.stdout + out.stderr
