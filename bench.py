@@ -223,9 +223,14 @@ def run_cuda(args) -> None:
     sync_after = {"v", "o", "up", "down"}
 
     def step():
+        pending = False  # a signal has been published that the next launch has to wait for
         for li in range(LAYERS):
             for pi, (name, t, _, k, act) in enumerate(PROJECTIONS):
-                if gather == "peer":
+                if gather == "peer" and args.order == "kernel":
+                    sig = name in sync_after
+                    peer_layers[li][pi](x_dev[k], None, act_types[act], wait=pending, signal=sig)
+                    pending = sig
+                elif gather == "peer":
                     peer_layers[li][pi](x_dev[k], None, act_types[act])
                     if name in sync_after:
                         bufs.barrier()
@@ -242,6 +247,13 @@ def run_cuda(args) -> None:
                     pass  # computed together with q / gate
                 else:
                     g.backend_fused_quantized_dense(x_dev[k], weights[li][pi], None, quant[t], acts[act], out=y_loc[li][pi])
+
+    if gather == "peer" and args.order == "kernel":
+        _inner = step
+
+        def step():  # close the step: the last signal is consumed by a device barrier, not by a next launch
+            _inner()
+            bufs.barrier()
 
     def select(pred):
         def run():
@@ -338,7 +350,7 @@ def run_cuda(args) -> None:
         "config": {"workload": WORKLOAD, "batch": batch, "weight_bytes_per_step": total_bytes,
                    "parallelism": f"rows/{world}" + {"none": "", "nccl": " + NCCL all-gather per projection",
                                                            "peer": " + all-gather fused into the GEMV epilogue (NVLink peer stores), "
-                                                                   "4 device barriers per layer"}[gather],
+                                                                   ("4 device barriers per layer" if args.order == "barrier" else "ranks ordered inside the kernels at 4 points per layer")}[gather],
                    "inputs": "fixed N(0,1) activations per projection (outputs not chained)",
                    "l2": f"no flush: {local_bytes / 1e6:.0f} MB of weights per GPU per step exceed the 126 MB L2",
                    "launch": ("one CUDA graph per step; q+k and gate+up of a layer share one launch each (160 launches)"
@@ -382,6 +394,9 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--fuse-shared-input", type=int, default=1,
                     help="1: q+k and gate+up (same activations, format and K) run as one launch each")
+    ap.add_argument("--order", default="barrier", choices=["barrier", "kernel"],
+                    help="N > 1 with --gather peer: order the ranks with device barriers between launches (default) "
+                         "or with completion counters inside the GEMV kernels (experimental)")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"], help="N > 1: how outputs are all-gathered")
     ap.add_argument("--traffic", type=float, default=None, help="dram bytes per launch of the dominant kernel (ncu)")
     args = ap.parse_args()

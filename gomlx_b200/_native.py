@@ -13,6 +13,7 @@ from .build import LIB_PATH
 OK, EINVAL, ENOTIMPL, ECUDA, ENOMEM, ETIMEOUT, EHANDLE = 0, -1, -2, -3, -4, -5, -6
 F32, BF16 = 0, 1
 KERNEL_NONE, KERNEL_GEMV_MMA, KERNEL_GEMM_TCGEN05 = 0, 1, 2
+SYNC_WAIT, SYNC_SIGNAL = 1, 2
 
 # Every symbol include/b200q.h declares: name -> (restype, argtypes)
 _i, _i64, _vp, _sz = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p, ctypes.c_size_t
@@ -35,7 +36,8 @@ SYMBOLS = {
     "b200q_dequantize": (_i, [_u64, _vp, _vp]),
     "b200q_dense": (_i, [_u64, _vp, _i, _i64, _vp, _i, _vp, _i64, _vp]),
     "b200q_dense_batch": (_i, [_i, _pu64, _vp, _i, _i64, ctypes.POINTER(_vp), _pi, ctypes.POINTER(_vp), _pi64, _vp]),
-    "b200q_dense_scatter": (_i, [_u64, _vp, _i, _i64, _vp, _i, _vp, ctypes.POINTER(_vp), _i, _i64, _i64, _vp]),
+    "b200q_dense_scatter": (_i, [_u64, _vp, _i, _i64, _vp, _i, _vp, ctypes.POINTER(_vp), _i, _i64, _i64,
+                                 _vp, ctypes.POINTER(_vp), _i, _i, _vp]),
     "b200q_dense_f32_prefill_noalloc": (_i, [_u64, _vp, _i64, _vp, _i, _vp, _i64, _vp]),
     "b200q_noalloc_capacity": (_i64, []),
     "b200q_embedding_lookup": (_i, [_u64, _vp, _i64, _vp, _vp]),

@@ -262,7 +262,8 @@ int b200q_dense_batch(int count, const b200q_weight_t *hs, const void *x_dev, in
 }
 
 int b200q_dense_scatter(b200q_weight_t h, const void *x_dev, int x_dtype, int64_t m, const float *bias_dev, int activation,
-                        float *y_local, float *const *y_peers, int n_peers, int64_t y_ld, int64_t row_offset, void *stream) {
+                        float *y_local, float *const *y_peers, int n_peers, int64_t y_ld, int64_t row_offset,
+                        int *sync_local, int *const *sync_peers, int rank, int sync_flags, void *stream) {
     auto w = find(h);
     if (!w) return fail(B200Q_EHANDLE, "dense_scatter: unknown handle");
     if (m == 0) return B200Q_OK;
@@ -271,12 +272,14 @@ int b200q_dense_scatter(b200q_weight_t h, const void *x_dev, int x_dtype, int64_
     if (x_dtype != B200Q_F32 && x_dtype != B200Q_BF16) return fail(B200Q_EINVAL, "dense_scatter: x dtype must be f32 or bf16");
     if (activation < B200Q_ACT_NONE || activation > B200Q_ACT_TANH) return fail(B200Q_EINVAL, "dense_scatter: bad activation");
     if (n_peers < 0 || n_peers > 7) return fail(B200Q_EINVAL, "dense_scatter: at most 7 peers");
+    if (sync_flags != 0 && (sync_local == nullptr || (n_peers > 0 && sync_peers == nullptr) || rank < 0 || rank > n_peers))
+        return fail(B200Q_EINVAL, "dense_scatter: sync flags need the sync words of every rank and a valid rank");
     if (row_offset < 0 || y_ld < row_offset + w->n) return fail(B200Q_EINVAL, "dense_scatter: y_ld smaller than row_offset + N");
     if (reinterpret_cast<uintptr_t>(x_dev) & 15) return fail(B200Q_EINVAL, "dense_scatter: x must be 16-byte aligned");
     B200Q_CUDA(cudaSetDevice(w->device));
     g_last_kernel = B200Q_KERNEL_GEMV_MMA;
     return launch_gemv(*w, x_dev, x_dtype, (int)m, bias_dev, activation, y_local, y_ld, static_cast<cudaStream_t>(stream),
-                       y_peers, n_peers, row_offset);
+                       y_peers, n_peers, row_offset, sync_local, sync_peers, rank, sync_flags);
 }
 
 int b200q_dense_f32_prefill_noalloc(b200q_weight_t h, const float *x_dev, int64_t m, const float *bias_dev,

@@ -73,6 +73,14 @@ struct GemvParams {
     const void *x;
     float *y_peer[7];  // the same output buffer on the other GPUs of a row-sharded layer (NVLink peer memory)
     int npeers;        // number of valid entries in y_peer
+    // Cross-GPU ordering without extra launches.  Each rank owns a small word array in peer-mapped memory:
+    // [r] = number of "signal" kernels rank r has completed (written by rank r), [8] = this rank's own
+    // count, [9] = CTAs of the running kernel that have finished.  A kernel launched with kSyncSignal
+    // publishes its completion to every rank after its last store; one launched with kSyncWait does not
+    // read activations or write outputs until every rank has published as many completions as this rank.
+    int *sync_local;
+    int *sync_peer[7];
+    int rank, sync_flags;
     int *status;
     int64_t k;
     int64_t row_off;   // first output column of this shard inside the full [m, N_total] result
@@ -92,6 +100,8 @@ struct GemvParams {
 };
 
 constexpr int kSpinLimit = 1 << 22;
+constexpr int kSyncWait = 1, kSyncSignal = 2;
+constexpr int kSyncEpochWord = 8, kSyncDoneWord = 9;
 
 #ifdef B200Q_TRACE
 // Diagnostic build only: per-CTA timestamps (ns) at five points of the kernel.
@@ -702,6 +712,22 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
     // Everything above touched only the immutable weights.  The activations may be the output of the
     // kernel before us in the stream, and our outputs may overwrite what it still reads: wait for it.
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if ((p.sync_flags & kSyncWait) && p.sync_local != nullptr) {
+        if (threadIdx.x == 0) {
+            const int expected = *reinterpret_cast<volatile int *>(p.sync_local + kSyncEpochWord);
+            bool all = false;
+            for (int spin = 0; spin < kSpinLimit && !all; spin++) {
+                all = true;
+                for (int r = 0; r <= p.npeers; r++) {
+                    int v;
+                    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p.sync_local + r) : "memory");
+                    all = all && (v - expected >= 0);
+                }
+            }
+            if (!all) atomicExch(p.status, 2);  // a peer never arrived: report, do not hang
+        }
+        __syncthreads();
+    }
     if (kt_begin < kt_end) stage_x<TYPE>(p, (int64_t)kt_begin * F::TK, (kt_end - kt_begin) * F::TK, xs_stride, ns, xs, shi, slo);
     __syncthreads();
     if (lane == 0)
@@ -800,6 +826,22 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
         }
     }
     if (p.splits > 1) cluster.sync();  // keep shared memory alive until every peer has read it
+    if ((p.sync_flags & kSyncSignal) && p.sync_local != nullptr) {
+        __syncthreads();  // this CTA's stores, local and remote, are issued
+        if (threadIdx.x == 0) {
+            __threadfence_system();
+            const int done = atomicAdd(p.sync_local + kSyncDoneWord, 1);
+            if (done == (int)gridDim.x - 1) {  // last CTA of the kernel: publish the new completion count
+                __threadfence_system();
+                p.sync_local[kSyncDoneWord] = 0;
+                const int e = p.sync_local[kSyncEpochWord] + 1;
+                p.sync_local[kSyncEpochWord] = e;
+                asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.sync_local + p.rank), "r"(e) : "memory");
+                for (int pr = 0; pr < p.npeers; pr++)
+                    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.sync_peer[pr] + p.rank), "r"(e) : "memory");
+            }
+        }
+    }
     B200Q_TRACE_POINT(5);
 }
 
@@ -948,7 +990,7 @@ int launch_nb(const Weight &w, const GemvParams &p, cudaStream_t s) {
 
 int launch_gemv_batch(int count, const Weight *const *ws, const void *x, int x_dtype, int m, const float *const *biases,
                       const int *acts, float *const *ys, const int64_t *y_lds, cudaStream_t s, float *const *y_peers,
-                      int npeers, int64_t row_off) {
+                      int npeers, int64_t row_off, int *sync_local, int *const *sync_peers, int rank, int sync_flags) {
     if (m < 1 || m > 16) return fail(B200Q_EINVAL, "gemv: m must be in 1..16");
     if (count < 1 || count > kMaxSegments) return fail(B200Q_EINVAL, "gemv: 1..4 matrices per launch");
     if (npeers < 0 || npeers > 7 || (npeers > 0 && (y_peers == nullptr || count != 1)))
@@ -970,6 +1012,9 @@ int launch_gemv_batch(int count, const Weight *const *ws, const void *x, int x_d
     for (int i = 0; i < npeers; i++) p.y_peer[i] = y_peers[i];
     p.npeers = npeers;
     p.row_off = row_off;
+    p.sync_local = sync_local;
+    for (int i = 0; i < npeers && sync_peers != nullptr; i++) p.sync_peer[i] = sync_peers[i];
+    p.rank = rank, p.sync_flags = (sync_local != nullptr && (npeers == 0 || sync_peers != nullptr)) ? sync_flags : 0;
     p.k = all.k;
     p.rt = all.rt, p.kt = all.kt;
     p.m = m, p.x_dtype = x_dtype;
@@ -984,11 +1029,13 @@ int launch_gemv_batch(int count, const Weight *const *ws, const void *x, int x_d
 }
 
 int launch_gemv(const Weight &w, const void *x, int x_dtype, int m, const float *bias, int act, float *y, int64_t y_ld,
-                cudaStream_t s, float *const *y_peers, int npeers, int64_t row_off) {
+                cudaStream_t s, float *const *y_peers, int npeers, int64_t row_off, int *sync_local, int *const *sync_peers,
+                int rank, int sync_flags) {
     const Weight *ws[1] = {&w};
     const float *biases[1] = {bias};
     float *ys[1] = {y};
-    return launch_gemv_batch(1, ws, x, x_dtype, m, biases, &act, ys, &y_ld, s, y_peers, npeers, row_off);
+    return launch_gemv_batch(1, ws, x, x_dtype, m, biases, &act, ys, &y_ld, s, y_peers, npeers, row_off, sync_local,
+                             sync_peers, rank, sync_flags);
 }
 
 }  // namespace b200q

@@ -86,17 +86,26 @@ class PeerScatterBuffers:
     every store issued before it on any rank is visible to every rank.
     """
 
+    SYNC_WORDS = 64  # the first 256 bytes of every rank's buffer hold the cross-GPU sync words
+
     def __init__(self, floats: int, device: int, group: Optional[dist.ProcessGroup] = None):
         import torch.distributed._symmetric_memory as symm_mem
         group = group if group is not None else dist.group.WORLD
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
-        self.local = symm_mem.empty(floats, dtype=torch.float32, device=torch.device("cuda", device))
-        self.handle = symm_mem.rendezvous(self.local, group.group_name)
+        self._all = symm_mem.empty(floats + self.SYNC_WORDS, dtype=torch.float32, device=torch.device("cuda", device))
+        self.handle = symm_mem.rendezvous(self._all, group.group_name)
         self._ptrs = [int(p) for p in self.handle.buffer_ptrs]
-        self.local.zero_()
+        self._all.zero_()
+        self.local = self._all[self.SYNC_WORDS:]
+        torch.cuda.synchronize()
+        self.handle.barrier(channel=0)  # every rank's sync words are zero before anyone signals
+        torch.cuda.synchronize()
 
     def ptr(self, rank: int, offset: int = 0) -> int:
-        return self._ptrs[rank] + 4 * offset
+        return self._ptrs[rank] + 4 * (self.SYNC_WORDS + offset)
+
+    def sync_ptr(self, rank: int) -> int:
+        return self._ptrs[rank]
 
     def barrier(self) -> None:
         self.handle.barrier(channel=0)
@@ -122,9 +131,14 @@ class PeerScatterDense:
         peers = [buffers.ptr(r, offset) for r in range(buffers.world) if r != buffers.rank]
         self._peer_arr = (ctypes.c_void_p * max(1, len(peers)))(*peers)
         self._n_peers = len(peers)
+        self._sync_arr = (ctypes.c_void_p * max(1, len(peers)))(
+            *[buffers.sync_ptr(r) for r in range(buffers.world) if r != buffers.rank])
         self.y = buffers.local[offset:offset + max_m * self.n_total].view(max_m, self.n_total)
 
-    def __call__(self, x: torch.Tensor, bias=None, activation: Activation = Activation.NONE) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, bias=None, activation: Activation = Activation.NONE, wait: bool = False,
+                 signal: bool = False) -> torch.Tensor:
+        """``signal``: publish this kernel's completion to all ranks; ``wait``: do not start until every rank
+        has published as many completions as this rank (in-kernel ordering, no extra launch)."""
         import ctypes
         from . import _native as nat
         x2 = x.reshape(-1, self.local.k).contiguous()
@@ -136,7 +150,9 @@ class PeerScatterDense:
             self.local.handle, ctypes.c_void_p(x2.data_ptr()), nat.F32 if x2.dtype == torch.float32 else nat.BF16, m,
             ctypes.c_void_p(b.data_ptr()) if b is not None else None, int(activation.to_backend()),
             ctypes.c_void_p(self.buffers.ptr(self.buffers.rank, self.offset)), self._peer_arr, self._n_peers,
-            self.n_total, self.local.row_begin, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+            self.n_total, self.local.row_begin, ctypes.c_void_p(self.buffers.sync_ptr(self.buffers.rank)), self._sync_arr,
+            self.buffers.rank, (1 if wait else 0) | (2 if signal else 0),
+            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
         return self.y[:m]
 
     def free(self) -> None:

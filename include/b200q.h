@@ -138,10 +138,21 @@ int b200q_dense_batch(int count, const b200q_weight_t *ws, const void *x_dev, in
  * [row_offset, row_offset + n) of an [N_total, K] matrix.  Every rank owns one [m, y_ld] f32 result
  * buffer; y_local is this rank's, y_peers[0..n_peers) are the other ranks' buffers mapped into this
  * process (CUDA peer / symmetric memory).  The epilogue stores each finished value at column
- * row_offset + n of y_local and of every peer buffer (plain stores over NVLink).  The caller orders the
- * ranks (a device-side barrier on the stream) before anyone reads the gathered result. */
+ * row_offset + n of y_local and of every peer buffer (plain stores over NVLink).
+ *
+ * Ordering between ranks, without extra launches: sync_local points to 16 zero-initialised int32 words in
+ * this rank's peer-mapped memory and sync_peers[i] to the same words of peer i (same order as y_peers);
+ * `rank` is this rank's index in 0..n_peers (every rank's peer list holds the other ranks).  With
+ * B200Q_SYNC_SIGNAL the kernel publishes its completion to all ranks after its last store; with
+ * B200Q_SYNC_WAIT it neither reads x nor writes y before every rank has published as many completions as
+ * this rank has.  The wait is bounded: if a peer never arrives the kernel records B200Q_ETIMEOUT
+ * (b200q_weight_check) and continues.  All ranks must issue the same sequence of flagged calls.  Pass
+ * sync_flags = 0 (and NULLs) to order the ranks by other means. */
+#define B200Q_SYNC_WAIT 1
+#define B200Q_SYNC_SIGNAL 2
 int b200q_dense_scatter(b200q_weight_t w, const void *x_dev, int x_dtype, int64_t m, const float *bias_dev, int activation,
-                        float *y_local, float *const *y_peers, int n_peers, int64_t y_ld, int64_t row_offset, void *stream);
+                        float *y_local, float *const *y_peers, int n_peers, int64_t y_ld, int64_t row_offset,
+                        int *sync_local, int *const *sync_peers, int rank, int sync_flags, void *stream);
 
 /* No counterpart in the reference: an allocation-free form of b200q_dense for prefill (m > 16) with f32
  * activations.  b200q_dense converts f32 activations to bf16 in a buffer it takes from the CUDA
