@@ -42,6 +42,14 @@ BPB = {12: 144, 14: 210}
 WORKLOAD = "llama3-8b-shaped decoder stack, 32 layers x 7 quantized projections (Q4_K; v/down Q6_K)"
 
 
+def host_threads() -> int:
+    """Host cores this process may use (torchrun exports OMP_NUM_THREADS=1, which is not the box's size)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def layer_weight_bytes() -> int:
     return sum(n * (k // 256) * BPB[t] for _, t, n, k, _ in PROJECTIONS)
 
@@ -134,7 +142,7 @@ def run_reference(args) -> None:
     if rank != 0:
         return
     from oracle import oracle as o
-    threads = o.max_threads()
+    threads = host_threads()
     for _ in range(max(0, min(args.warmup, 1))):
         cpu_sample(args.batch, 1, threads)
     times = []
@@ -365,7 +373,7 @@ def run_cuda(args) -> None:
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             from oracle import oracle as o  # checker timed as the CPU baseline; never on the product path
-            threads = o.max_threads()
+            threads = host_threads()
             sec, nbytes = cpu_sample(batch, 2, threads)
             out["cpu_baseline"] = {"value": nbytes / sec / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
                                    "sample": f"1 of {LAYERS} layers (7 projections, {nbytes} weight bytes), 2 passes, "
