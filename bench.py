@@ -357,7 +357,7 @@ def run_cuda(args) -> None:
         "vs_baseline": None, "dtype": "f16 multiply / f32 accumulate on packed u8 blocks", "data": "synthetic",
         "config": {"workload": WORKLOAD, "batch": batch, "weight_bytes_per_step": total_bytes,
                    "parallelism": f"rows/{world}" + {"none": "", "nccl": " + NCCL all-gather per projection",
-                                                           "peer": " + all-gather fused into the GEMV epilogue (NVLink peer stores), "
+                                                           "peer": " + all-gather fused into the GEMV epilogue (NVLink peer stores), " +
                                                                    ("4 device barriers per layer" if args.order == "barrier" else "ranks ordered inside the kernels at 4 points per layer")}[gather],
                    "inputs": "fixed N(0,1) activations per projection (outputs not chained)",
                    "l2": f"no flush: {local_bytes / 1e6:.0f} MB of weights per GPU per step exceed the 126 MB L2",
