@@ -170,6 +170,19 @@ def test_gemm_parity(oracle, name, m, n, k, dtype):
     wr.free()
 
 
+@pytest.mark.parametrize("name", ["Q8_0", "Q4_0"])
+def test_gemm_ragged_k(oracle, name):
+    """K = 41 blocks of 32: not a multiple of the 64-wide MMA stage nor of the 256-value tile."""
+    t = TYPES[name]
+    m, n, k = 70, 130, 1312
+    w = oracle.make_weights(int(t), n, k, seed=5)
+    x = torch.from_numpy(np.random.default_rng(3).standard_normal((m, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    ref = oracle.dense(int(t), w, x.float().cpu().numpy(), route="f64")
+    y = g.quantized_dense(x, w, quant(t))
+    assert g.last_kernel() == nat.KERNEL_GEMM_TCGEN05
+    assert rel_err(y.cpu().numpy(), ref) <= TOL_GEMM
+
+
 def test_gemm_prefill_config_shapes(oracle):
     """configs[2]: Q4_K, x bf16 [512, 4096], W 4096 x 4096 (oracle on all rows) and 4096 x 14336 (sampled rows)."""
     t = g.GGMLQuantType.Q4_K
