@@ -43,19 +43,22 @@ template <> struct Depth<kQ6_K> { static constexpr int SA = 6, SB = 4, SP = 2; }
 constexpr int kGemmSpinLimit = 1 << 24;
 
 #ifdef B200Q_TRACE
-// Diagnostic build only: timestamps (ns) of CTA 0, [role][stage][point].
+// Diagnostic build only: SM cycle counter of CTA 0, [role][stage][point].
 __device__ unsigned long long *g_gemm_trace = nullptr;
 __device__ __forceinline__ unsigned long long gemm_now() {
     unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t));
     return t;
 }
+#define GEMM_TRACE_INIT() unsigned long long *const gtrace = (blockIdx.x == 0 && blockIdx.y == 0) ? g_gemm_trace : nullptr
 #define GEMM_TRACE(role, stage, point)                                                                   \
     do {                                                                                                  \
-        if (g_gemm_trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (stage) < 256)              \
-            g_gemm_trace[((role) * 256 + (stage)) * 4 + (point)] = gemm_now();                            \
+        if (gtrace != nullptr && (stage) < 256) gtrace[((role) * 256 + (stage)) * 4 + (point)] = gemm_now(); \
     } while (0)
 #else
+#define GEMM_TRACE_INIT() \
+    do {                  \
+    } while (0)
 #define GEMM_TRACE(role, stage, point) \
     do {                               \
     } while (0)
@@ -94,6 +97,24 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *st
             : "r"(bar), "r"(parity)
             : "memory");
         if (ok) return true;
+    }
+    atomicExch(status, 2);
+    return false;
+}
+// The same for waiters that are not on the critical path (a ring slot many stages ahead): they sleep
+// between polls, so that their polling does not take issue slots from the MMA-issuing thread.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, int *status) {
+    for (int spin = 0; spin < (kGemmSpinLimit >> 4); spin++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        __nanosleep(64);
     }
     atomicExch(status, 2);
     return false;
@@ -281,6 +302,7 @@ template <int TYPE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
     using F = Fmt<TYPE>;
+    GEMM_TRACE_INIT();
     constexpr int SA = Depth<TYPE>::SA, SB = Depth<TYPE>::SB, SP = Depth<TYPE>::SP;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // carve: A stages | B stages | packed stages | barriers | tmem slot   (A/B need 1024-byte alignment)
@@ -462,6 +484,332 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Kernel with the dequantized weights as the MMA's tensor-memory operand.
+//
+// The roles of the operands are swapped with respect to the kernel above: D[weight row, batch row]
+// accumulates A = dequant(W) (128 weight rows = TMEM lanes, K packed two bf16 per 32-bit column)
+// times B = activations (BN batch rows x 64, K-major in shared memory, written by TMA).  The
+// dequantize warps write their values straight from registers into tensor memory (tcgen05.st), so
+// the dequantized tile never passes through shared memory, whose bandwidth the MMA needs for B.
+//
+// One CTA computes R row blocks of 128 weight rows x BN batch rows over all of K:
+//   R = 2, BN = 128   every activation stage feeds two MMAs (half the activation traffic per flop)
+//   R = 1, BN = 256   for m > 128: every dequantized value feeds 256 batch rows, which halves the
+//                     dequantize work per flop (the ALU pipes, not the tensor pipe, are the limit)
+//   R = 1, BN = 128   smallest tile, for problems with too few tiles to fill the GPU otherwise
+// TMEM: R*BN accumulator columns (<= 256), then a ring of operand stages of 32*R columns each (one
+// 64-wide k stage of every row block) in the other 256 columns.
+//
+// TMEM lane L of a row block holds weight row 16*(L & 7) + (L >> 3) of the block: consecutive
+// lanes of a dequantize warp then read the same piece of 8 different row tiles, and with the row
+// tiles placed 16 bytes further apart than their size those 8 reads hit 8 different bank groups.
+// The epilogue reads D with lanes = weight rows and undoes the permutation when it stores.
+// ---------------------------------------------------------------------------------------
+constexpr int kTmemCols = 512;
+
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint4 &a, const uint4 &b) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(a.x), "r"(a.y),
+                 "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint4 (&v)[4]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+        "r"(v[0].x), "r"(v[0].y), "r"(v[0].z), "r"(v[0].w), "r"(v[1].x), "r"(v[1].y), "r"(v[1].z), "r"(v[1].w), "r"(v[2].x),
+        "r"(v[2].y), "r"(v[2].z), "r"(v[2].w), "r"(v[3].x), "r"(v[3].y), "r"(v[3].z), "r"(v[3].w)
+        : "memory");
+}
+
+// 32 consecutive values (group kq of the 256-value tile, row r): out[c] holds values 8c .. 8c+7.
+template <int TYPE>
+__device__ __forceinline__ void dequant32(uint32_t tile, int r, int kq, uint4 (&out)[4]) {
+    const int g = r & 7, rs = r >> 3;
+    if constexpr (TYPE == kQ4_0) {
+        const int t = kq >> 1, bp = kq & 1;
+        const float d = h16(lds16(tile + r * 16 + kq * 2));
+        const uint4 q = lds128(tile + 256 + (2 * bp + rs) * 512 + (4 * g + t) * 16);
+        const float ol = -1032.0f * d, oh = -72.0f * d;
+        out[0] = nibble_chunk<false>(q.x, q.y, d, ol);
+        out[1] = nibble_chunk<false>(q.z, q.w, d, ol);
+        out[2] = nibble_chunk<true>(q.x, q.y, d, oh);
+        out[3] = nibble_chunk<true>(q.z, q.w, d, oh);
+    } else if constexpr (TYPE == kQ8_0) {
+        const int t = kq >> 1, bp = kq & 1;
+        const float d = h16(lds16(tile + r * 16 + kq * 2));
+        const float o = -1152.0f * d;
+#pragma unroll
+        for (int sub = 0; sub < 2; sub++) {
+            const uint4 a = lds128(tile + 256 + (2 * (2 * bp + sub) + rs) * 512 + (4 * g + t) * 16);
+            out[2 * sub] = byte_chunk(a.x ^ 0x80808080u, a.y ^ 0x80808080u, d, o);
+            out[2 * sub + 1] = byte_chunk(a.z ^ 0x80808080u, a.w ^ 0x80808080u, d, o);
+        }
+    } else if constexpr (TYPE == kQ4_K) {
+        const int G = kq >> 1, hi = kq & 1;
+        const uint4 h = lds128(tile + r * 16);
+        const float d = h16(h.x & 0xFFFFu), dmin = h16(h.x >> 16);
+        uint32_t sc, mn;
+        if (kq < 4) {
+            sc = (h.y >> (8 * kq)) & 63u;
+            mn = (h.z >> (8 * kq)) & 63u;
+        } else {
+            const int j = kq - 4;
+            sc = ((h.w >> (8 * j)) & 0x0Fu) | (((h.y >> (8 * j + 6)) & 3u) << 4);
+            mn = ((h.w >> (8 * j + 4)) & 0x0Fu) | (((h.z >> (8 * j + 6)) & 3u) << 4);
+        }
+        const float ds = d * (float)sc, dm = dmin * (float)mn;
+        const float o = fmaf(hi ? -64.0f : -1024.0f, ds, -dm);
+#pragma unroll
+        for (int sub = 0; sub < 2; sub++) {
+            const uint4 q = lds128(tile + 256 + (2 * sub + rs) * 512 + (4 * g + G) * 16);
+            if (hi) {
+                out[2 * sub] = nibble_chunk<true>(q.x, q.y, ds, o);
+                out[2 * sub + 1] = nibble_chunk<true>(q.z, q.w, ds, o);
+            } else {
+                out[2 * sub] = nibble_chunk<false>(q.x, q.y, ds, o);
+                out[2 * sub + 1] = nibble_chunk<false>(q.z, q.w, ds, o);
+            }
+        }
+    } else {
+        uint4 half[2];
+        dequant16<TYPE>(tile, r, kq, 0, half);
+        out[0] = half[0], out[1] = half[1];
+        dequant16<TYPE>(tile, r, kq, 1, half);
+        out[2] = half[0], out[3] = half[1];
+    }
+}
+
+// Issues the MMAs of k-steps K0 .. K1-1 of one stage for every row block in ONE asm statement, so that
+// the issuing thread spends two additions per MMA and nothing else.  `first` = 0 makes the very first
+// MMA (k-step 0) overwrite the accumulator instead of adding to it.
+template <int R, int BNB, int K0, int K1>
+__device__ __forceinline__ void issue_mmas(uint32_t tmem_d, uint32_t alo, uint32_t xlo, uint32_t xhi, uint32_t idesc,
+                                           uint32_t first) {
+#pragma unroll
+    for (int k = K0; k < K1; k++) {
+#pragma unroll
+        for (int h = 0; h < R; h++) {
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t.reg .b64 bd;\n\t"
+                "setp.ne.b32 p, %5, 0;\n\t"
+                "mov.b64 bd, {%2, %3};\n\t"
+                "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %4, p;\n\t}" ::"r"(tmem_d + h * BNB),
+                "r"(alo + 32 * h + 8 * k), "r"(xlo + 2 * k), "r"(xhi), "r"(idesc), "r"(k == 0 ? first : 1u)
+                : "memory");
+        }
+    }
+}
+
+// Shared-memory budget: activation stages of BN x 64 bf16 and packed stages of 8*R padded row tiles.
+template <int TYPE, int R, int BNB> struct TmemCfg {
+    static constexpr int TILE_PITCH = Fmt<TYPE>::TILE + 16;
+    static constexpr int X_BYTES = BNB * BK * 2;
+    static constexpr int P_BYTES = 8 * R * TILE_PITCH;
+    static constexpr int SP = (P_BYTES > 30000) ? 2 : 3;
+    static constexpr int A_COLS = 32 * R;                 // TMEM columns of one operand stage
+    // One ring for both operands of a k stage: activation tile in shared memory, weights in TMEM.
+    static constexpr int S_FIT = (225 * 1024 - 1024 - SP * P_BYTES - 512) / X_BYTES;
+    static constexpr int S_TMEM = 256 / A_COLS;
+    static constexpr int S = S_FIT < S_TMEM ? S_FIT : S_TMEM;
+    static constexpr int NBAR = 2 * S + 2 * SP + 1;
+    static constexpr size_t SMEM = 1024 + (size_t)S * X_BYTES + (size_t)SP * P_BYTES + 8 * NBAR + 16;
+    static_assert(S >= 3, "stage ring too shallow");
+    static_assert(R * BNB <= 256, "accumulators must fit in half of TMEM");
+};
+
+template <int TYPE, int R, int BNB>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tmem_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
+    using F = Fmt<TYPE>;
+    using C = TmemCfg<TYPE, R, BNB>;
+    GEMM_TRACE_INIT();
+    constexpr int S = C::S, SP = C::SP, RT = 8 * R;
+    constexpr uint32_t X_BYTES = C::X_BYTES, P_BYTES = C::P_BYTES, TILE_PITCH = C::TILE_PITCH;
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BNB >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t x_s = smem_u32(smem), p_s = x_s + S * X_BYTES, bar_s = p_s + SP * P_BYTES;
+    // full[s]: the activation tile has landed (producer's arrive + TMA bytes) and all 16 dequantize warps
+    // have stored their share of the weight operand; empty[s]: the MMAs that read stage s have completed.
+    // One barrier per direction keeps the MMA-issuing thread at one wait and one commit per stage: each
+    // costs it about 200 cycles, which the queued MMAs of a stage have to cover.
+    const uint32_t full = bar_s, empty = full + 8 * S, p_full = empty + 8 * S, p_empty = p_full + 8 * SP;
+    const uint32_t d_full = p_empty + 8 * SP;
+    const uint32_t tmem_slot = d_full + 8;
+    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(smem + (tmem_slot - x_s));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t m0 = (int64_t)blockIdx.y * BNB;
+    const int64_t rt0 = (int64_t)blockIdx.x * RT;
+    const int nrt = (int)min((int64_t)RT, p.rt - rt0);  // row tiles that exist in this CTA's rows
+    const int nkt = (int)p.kt, nst = nkt * 4;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < S; i++) mbar_init(full + 8 * i, kDequantWarps + 1), mbar_init(empty + 8 * i, 1);
+        for (int i = 0; i < SP; i++) mbar_init(p_full + 8 * i, 1), mbar_init(p_empty + 8 * i, kDequantWarps);
+        mbar_init(d_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = *tmem_slot_ptr;   // accumulators: row block h in columns h*BNB ..
+    const uint32_t tmem_a = tmem_d + 256;     // operand ring
+
+    if (warp == 0) {
+        if (lane == 0) {  // activation producer
+            uint32_t sx = 0, ph = 1;
+            for (int ks = 0; ks < nst; ks++) {
+                if (!mbar_wait_relaxed(empty + 8 * sx, ph, p.status)) break;
+                mbar_expect_tx(full + 8 * sx, X_BYTES);
+                tma_load_2d(x_s + sx * X_BYTES, &xmap, ks * BK, (int)m0, full + 8 * sx);
+                if (++sx == S) sx = 0, ph ^= 1;
+            }
+        }
+    } else if (warp == 2) {
+        if (lane == 0) {  // packed-weight producer: one stage = one 256-value tile of every row tile
+            uint32_t sp = 0, ph = 1;
+            const uint8_t *src = p.tiles + rt0 * p.kt * (int64_t)F::TILE;
+            const int64_t row_stride = p.kt * (int64_t)F::TILE;
+            for (int kt = 0; kt < nkt; kt++) {
+                if (!mbar_wait_relaxed(p_empty + 8 * sp, ph, p.status)) break;
+                mbar_expect_tx(p_full + 8 * sp, nrt * F::TILE);
+                for (int i = 0; i < nrt; i++)
+                    bulk_load(p_s + sp * P_BYTES + i * TILE_PITCH, src + i * row_stride, F::TILE, p_full + 8 * sp);
+                src += F::TILE;
+                if (++sp == SP) sp = 0, ph ^= 1;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // MMA issuer.  Issuing an MMA blocks until the tensor pipe accepts it, and the pipe's queue is
+            // short, so the waits for the next stage are done while the current stage still has MMAs to
+            // issue: only the two commits separate the last MMA of a stage from the first of the next.
+            uint32_t st = 0, ph = 0;
+            const uint64_t xd0 = umma_desc(x_s);
+            bool ok = mbar_wait(full, 0, p.status);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t xlo = (uint32_t)xd0, alo = tmem_a;   // descriptor low word / operand address of the current stage
+            const uint32_t xhi = (uint32_t)(xd0 >> 32);
+            for (int ks = 0; ks < nst && ok; ks++) {
+                GEMM_TRACE(1, ks, 0);
+                issue_mmas<R, BNB, 0, 3>(tmem_d, alo, xlo, xhi, IDESC, ks > 0 ? 1u : 0u);
+                GEMM_TRACE(1, ks, 1);
+                uint32_t nst_ = st + 1, nph = ph, nxlo = xlo + (X_BYTES >> 4), nalo = alo + C::A_COLS;
+                if (nst_ == S) nst_ = 0, nph ^= 1, nxlo = (uint32_t)xd0, nalo = tmem_a;
+                if (ks + 1 < nst) {
+                    ok = mbar_wait(full + 8 * nst_, nph, p.status);
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                }
+                GEMM_TRACE(1, ks, 2);
+                issue_mmas<R, BNB, 3, 4>(tmem_d, alo, xlo, xhi, IDESC, 1u);
+                umma_commit(empty + 8 * st);
+                GEMM_TRACE(1, ks, 3);
+                st = nst_, ph = nph, xlo = nxlo, alo = nalo;
+            }
+            umma_commit(d_full);
+        }
+    } else {
+        // dequantize: warp = (TMEM lane quarter rb, share idx of each 64-wide stage).
+        //   R = 2: idx = (row block h, 32-value half kh);  R = 1: idx = 16-value group
+        const int rb = warp & 3, idx = (warp - kFirstDequantWarp) >> 2;
+        const int h = R == 2 ? idx >> 1 : 0;
+        const int rtile = 8 * h + (lane & 7), r = 4 * rb + (lane >> 3);
+        const bool row_exists = rtile < nrt;
+        const uint32_t st_base = tmem_a + ((uint32_t)(32 * rb) << 16) + (R == 2 ? h * 32 + (idx & 1) * 16 : idx * 8);
+        bool ok = true;
+        uint32_t sp = 0, pp = 0, sa = 0, pa = 1;  // sa, pa: stage ring slot and the parity of its empty barrier
+        for (int kt = 0; kt < nkt && ok; kt++) {
+            ok = mbar_wait_relaxed(p_full + 8 * sp, pp, p.status);
+            const uint32_t tile = p_s + sp * P_BYTES + rtile * TILE_PITCH;
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                if (threadIdx.x == 32 * kFirstDequantWarp) GEMM_TRACE(2, kt * 4 + q, 0);
+                uint4 out[4];
+#ifdef B200Q_GEMM_FAKE_DEQUANT
+                if (false) {
+#else
+                if (row_exists && ok) {
+#endif
+                    if constexpr (R == 2) {
+                        dequant32<TYPE>(tile, r, 2 * q + (idx & 1), out);
+                    } else {
+                        uint4 half[2];
+                        dequant16<TYPE>(tile, r, 2 * q + (idx >> 1), idx & 1, half);
+                        out[0] = half[0], out[1] = half[1];
+                    }
+                } else {
+                    out[0] = out[1] = out[2] = out[3] = make_uint4(0u, 0u, 0u, 0u);
+                }
+                if (threadIdx.x == 32 * kFirstDequantWarp) GEMM_TRACE(2, kt * 4 + q, 1);
+                if (ok) ok = mbar_wait_relaxed(empty + 8 * sa, pa, p.status);
+                if (threadIdx.x == 32 * kFirstDequantWarp) GEMM_TRACE(2, kt * 4 + q, 2);
+#ifndef B200Q_GEMM_NO_ST
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if constexpr (R == 2) {
+                    tmem_st16(st_base + sa * C::A_COLS, out);
+                } else {
+                    tmem_st8(st_base + sa * C::A_COLS, out[0], out[1]);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+#endif
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full + 8 * sa);
+                if (threadIdx.x == 32 * kFirstDequantWarp) GEMM_TRACE(2, kt * 4 + q, 3);
+                if (lane == 0 && kt * 4 + q == 16) GEMM_TRACE(0, warp, 0);
+                if (lane == 0 && kt * 4 + q == 48) GEMM_TRACE(0, warp, 1);
+                if (++sa == S) sa = 0, pa ^= 1;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_empty + 8 * sp);
+            if (++sp == SP) sp = 0, pp ^= 1;
+        }
+        // epilogue: the R*BNB accumulator columns are split into four chunks, one per idx; a thread's TMEM
+        // lane is one weight row (one column of y), its registers are consecutive batch rows.
+        if (mbar_wait(d_full, 0, p.status)) {
+            if (threadIdx.x == 32 * kFirstDequantWarp) GEMM_TRACE(3, 0, 0);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            constexpr int CHUNK = R * BNB / 4;
+            const int c0 = idx * CHUNK, he = c0 / BNB, coff = c0 % BNB;
+            const int64_t col = (int64_t)blockIdx.x * (128 * R) + 128 * he + 16 * (lane & 7) + r;
+            const bool col_ok = col < p.n;
+            const float b = (p.bias != nullptr && col_ok) ? __ldg(p.bias + col) : 0.0f;
+#pragma unroll
+            for (int part = 0; part < CHUNK / 32; part++) {
+                uint32_t v[32];
+                tmem_ld32(tmem_d + ((uint32_t)(32 * rb) << 16) + c0 + 32 * part, v);
+                if (col_ok) {
+                    const int64_t row0 = m0 + coff + 32 * part;
+                    float *dst = p.y + row0 * p.y_ld + col;
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        if (row0 + j < p.m) dst[j * p.y_ld] = apply_activation(p.act, __uint_as_float(v[j]) + b);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    GEMM_TRACE(3, 0, 1);
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(kTmemCols) : "memory");
+    }
+}
+
 __global__ void f32_to_bf16_kernel(const float *__restrict__ src, __nv_bfloat16 *__restrict__ dst, int64_t n) {
     for (int64_t i = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * 4; i < n; i += (int64_t)gridDim.x * blockDim.x * 4) {
         const float4 v = *reinterpret_cast<const float4 *>(src + i);
@@ -485,24 +833,43 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-template <int TYPE>
-int launch_gemm_t(const Weight &w, const __nv_bfloat16 *x, int64_t m, const float *bias, int act, float *y, int64_t y_ld,
-                  cudaStream_t s) {
-    using F = Fmt<TYPE>;
+int encode_x_map(CUtensorMap *map, const __nv_bfloat16 *x, int64_t m, int64_t k, int box_rows) {
     EncodeTiledFn enc = encode_tiled();
     if (!enc) return fail(B200Q_ECUDA, "gemm: cuTensorMapEncodeTiled is not available");
-    CUtensorMap map;
-    const cuuint64_t dims[2] = {(cuuint64_t)w.k, (cuuint64_t)m};
-    const cuuint64_t strides[1] = {(cuuint64_t)w.k * 2};
-    const cuuint32_t box[2] = {BK, BM};
+    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
+    const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    const cuuint32_t box[2] = {BK, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    CUresult cr = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16 *>(x), dims, strides, box, estr,
+    CUresult cr = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16 *>(x), dims, strides, box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return fail(B200Q_ECUDA, "gemm: cuTensorMapEncodeTiled failed");
-    GemmParams p{};
-    p.tiles = w.tiles, p.bias = bias, p.y = y, p.status = w.status;
-    p.m = m, p.n = w.n, p.y_ld = y_ld, p.rt = w.rt, p.kt = w.kt, p.act = act;
+    return 0;
+}
+
+template <int TYPE, int R, int BNB>
+int launch_tmem(const Weight &w, const __nv_bfloat16 *x, int64_t m, const GemmParams &p, cudaStream_t s) {
+    using C = TmemCfg<TYPE, R, BNB>;
+    CUtensorMap map;
+    int rc = encode_x_map(&map, x, m, w.k, BNB);
+    if (rc != 0) return rc;
+    auto kern = gemm_tmem_kernel<TYPE, R, BNB>;
+    static thread_local bool configured[16] = {};
+    if (!configured[w.device & 15]) {
+        B200Q_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+        configured[w.device & 15] = true;
+    }
+    dim3 grid((unsigned)((w.n + 128 * R - 1) / (128 * R)), (unsigned)((m + BNB - 1) / BNB), 1);
+    kern<<<grid, kThreads, C::SMEM, s>>>(map, p);
+    return 0;
+}
+
+template <int TYPE>
+int launch_ss(const Weight &w, const __nv_bfloat16 *x, int64_t m, const GemmParams &p, cudaStream_t s) {
+    using F = Fmt<TYPE>;
+    CUtensorMap map;
+    int rc = encode_x_map(&map, x, m, w.k, BM);
+    if (rc != 0) return rc;
     constexpr int SA = Depth<TYPE>::SA, SB = Depth<TYPE>::SB, SP = Depth<TYPE>::SP;
     const size_t smem = 1024 + SA * BM * BK * 2 + SB * BN * BK * 2 + SP * 8 * F::TILE + 8 * (2 * SA + 2 * SB + 2 * SP + 1) + 16;
     auto kern = gemm_tcgen05_kernel<TYPE>;
@@ -513,6 +880,34 @@ int launch_gemm_t(const Weight &w, const __nv_bfloat16 *x, int64_t m, const floa
     }
     dim3 grid((unsigned)((w.n + BN - 1) / BN), (unsigned)((m + BM - 1) / BM), 1);
     kern<<<grid, kThreads, smem, s>>>(map, p);
+    return 0;
+}
+
+// Tile shape: 0 = shared-memory operand kernel, 1 = R1 x 128, 2 = R2 x 128, 3 = R1 x 256.
+int choose_shape(const Weight &w, int64_t m) {
+    static const int forced = [] {
+        const char *e = getenv("B200Q_GEMM_SHAPE");
+        return e != nullptr ? atoi(e) : -1;
+    }();
+    if (forced >= 0) return forced;
+    if (m > 128) return 3;
+    return (w.n + 127) / 128 > 2 * 148 ? 2 : 1;
+}
+
+template <int TYPE>
+int launch_gemm_t(const Weight &w, const __nv_bfloat16 *x, int64_t m, const float *bias, int act, float *y, int64_t y_ld,
+                  cudaStream_t s) {
+    GemmParams p{};
+    p.tiles = w.tiles, p.bias = bias, p.y = y, p.status = w.status;
+    p.m = m, p.n = w.n, p.y_ld = y_ld, p.rt = w.rt, p.kt = w.kt, p.act = act;
+    int rc;
+    switch (choose_shape(w, m)) {
+    case 0: rc = launch_ss<TYPE>(w, x, m, p, s); break;
+    case 1: rc = launch_tmem<TYPE, 1, 128>(w, x, m, p, s); break;
+    case 2: rc = launch_tmem<TYPE, 2, 128>(w, x, m, p, s); break;
+    default: rc = launch_tmem<TYPE, 1, 256>(w, x, m, p, s); break;
+    }
+    if (rc != 0) return rc;
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : cuda_fail(e, "gemm launch");
 }
