@@ -1,17 +1,18 @@
-// Prefill GEMM (m > 16) for GGML block-quantized weights on sm_100a: tcgen05 MMA with TMEM
-// accumulators, the packed weights dequantized on the fly into the MMA's shared-memory operand.
+// Prefill GEMM (m > 16) for GGML block-quantized weights on sm_100a: tcgen05 MMA with the packed
+// weights dequantized on the fly into the MMA's tensor-memory operand and f32 accumulators in TMEM.
 //
 // Computes compute.Function.FusedQuantizedDense (core/graph/fused_ops.go:195-245 in gomlx/gomlx):
 //     y[m, n] = act(sum_k x[m, k] * dequant(W)[n, k] + bias[n])
 //
-// One CTA computes a 128 (batch rows) x 128 (weight rows) tile of y over all of K.
-//   warp 0      TMA tensor loads of the bf16 activation tile (128 x 64, 128-byte swizzle)
-//   warp 2      TMA bulk copies of the packed weight tiles (8 row tiles x 256 values per stage)
-//   warp 1      allocates TMEM and issues tcgen05.mma (one elected lane): D[128 x 128] f32 in TMEM,
-//               A = activations, B = dequantized weights, both K-major bf16 in shared memory
-//   warps 3-18  dequantize: thread (weight row, quarter) turns 16 packed values per 64-wide k stage into
-//               bf16 and writes them in the UMMA 128-byte-swizzled K-major layout; afterwards the same
-//               warps read the accumulator back with tcgen05.ld and apply bias / activation
+// One CTA computes 128 or 256 weight rows x 128 or 256 batch rows of y over all of K (three tile
+// shapes, see gemm_tmem_kernel).  19 warps:
+//   warp 0      TMA tensor loads of the bf16 activation tile (batch rows x 64, 128-byte swizzle)
+//   warp 2      TMA bulk copies of the packed weight tiles (256 values of every row tile per stage)
+//   warp 1      allocates TMEM and issues tcgen05.mma (one lane): D[weight row, batch row] f32 in TMEM,
+//               A = dequantized weights in TMEM, B = activations K-major bf16 in shared memory
+//   warps 3-18  dequantize: a thread owns one weight row (= its TMEM lane), turns 16 or 32 packed values
+//               per 64-wide k stage into bf16 and stores them into TMEM with tcgen05.st; afterwards the
+//               same warps read the accumulator back with tcgen05.ld and apply bias / activation
 // All hand-offs go through mbarriers; every wait is bounded and records a timeout in the weight's
 // status word instead of spinning forever.
 //
@@ -29,17 +30,11 @@
 namespace b200q {
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64;
+constexpr int BK = 64;   // k stage: one 128-byte swizzle atom of bf16
 constexpr int kDequantWarps = 16;
 constexpr int kFirstDequantWarp = 3;     // warps 0, 1, 2: activation TMA, MMA issue, packed-weight TMA
 constexpr int kThreads = 32 * (kFirstDequantWarp + kDequantWarps);
 
-// Pipeline depths per format: activation stages (16 KB), dequantized weight stages (16 KB), packed
-// weight stages (8 tiles).  A TMA load from L2 takes about a microsecond and one stage of MMAs about
-// 0.15 us, so the activation ring has to be deep; the sizes below fill the 227 KB of shared memory.
-template <int TYPE> struct Depth { static constexpr int SA = 6, SB = 4, SP = 3; };           // Q4_0, Q4_K: 2304-byte tiles
-template <> struct Depth<kQ8_0> { static constexpr int SA = 5, SB = 3, SP = 2; };            // 4352-byte tiles
-template <> struct Depth<kQ6_K> { static constexpr int SA = 6, SB = 4, SP = 2; };            // 3360-byte tiles
 constexpr int kGemmSpinLimit = 1 << 24;
 
 #ifdef B200Q_TRACE
@@ -141,16 +136,6 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
     d |= (uint64_t)2 << 61;                  // SWIZZLE_128B
     return d;
 }
-// Instruction descriptor: D f32, A and B bf16, both K-major, M = 128, N = 128.
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate)
-        : "memory");
-}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -187,10 +172,6 @@ __device__ __forceinline__ uint32_t lds8(uint32_t addr) {
     asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
 }
-__device__ __forceinline__ void sts128(uint32_t addr, const uint4 &v) {
-    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
-
 
 // ---------------------------------------------------------------------------------------
 // Dequantization of 32 consecutive values (group kq = 0..7 of a 256-value tile) of tile row r
@@ -298,192 +279,6 @@ __device__ __forceinline__ void dequant16(uint32_t tile, int r, int kq, int sub,
     }
 }
 
-template <int TYPE>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
-    using F = Fmt<TYPE>;
-    GEMM_TRACE_INIT();
-    constexpr int SA = Depth<TYPE>::SA, SB = Depth<TYPE>::SB, SP = Depth<TYPE>::SP;
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    // carve: A stages | B stages | packed stages | barriers | tmem slot   (A/B need 1024-byte alignment)
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, P_BYTES = 8 * F::TILE;
-    const uint32_t a_s = smem_u32(smem), b_s = a_s + SA * A_BYTES, p_s = b_s + SB * B_BYTES;
-    const uint32_t bar_s = p_s + SP * P_BYTES;
-    // barrier indices
-    const uint32_t a_full = bar_s, a_empty = a_full + 8 * SA, b_full = a_empty + 8 * SA, b_empty = b_full + 8 * SB;
-    const uint32_t p_full = b_empty + 8 * SB, p_empty = p_full + 8 * SP, d_full = p_empty + 8 * SP;
-    const uint32_t tmem_slot = d_full + 8;
-    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(smem + (tmem_slot - a_s));
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t m0 = (int64_t)blockIdx.y * BM;
-    const int64_t rt0 = (int64_t)blockIdx.x * (BN / 16);
-    const int nrt = (int)min((int64_t)(BN / 16), p.rt - rt0);  // row tiles that exist in this column tile
-    const int64_t nstages = p.kt * 4;                            // 64-wide k stages
-
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < SA; i++) mbar_init(a_full + 8 * i, 1), mbar_init(a_empty + 8 * i, 1);
-        for (int i = 0; i < SB; i++) mbar_init(b_full + 8 * i, kDequantWarps), mbar_init(b_empty + 8 * i, 1);
-        for (int i = 0; i < SP; i++) mbar_init(p_full + 8 * i, 1), mbar_init(p_empty + 8 * i, kDequantWarps);
-        mbar_init(d_full, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    if (warp == 1) {  // TMEM: 128 columns of f32 accumulators
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(BN) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_d = *tmem_slot_ptr;
-
-    // The three single-thread loops below are the pacemakers of the pipeline; they use 32-bit ring
-    // counters and phase bits (no divisions) so that one trip takes tens, not hundreds, of cycles.
-    const int nst = (int)nstages, nkt = (int)p.kt;
-    if (warp == 0) {
-        if (lane == 0) {  // activation producer
-            uint32_t sa = 0, ph = 1;
-            for (int ks = 0; ks < nst; ks++) {
-                if (!mbar_wait(a_empty + 8 * sa, ph, p.status)) break;
-                GEMM_TRACE(0, ks, 0);
-                mbar_expect_tx(a_full + 8 * sa, A_BYTES);
-                tma_load_2d(a_s + sa * A_BYTES, &xmap, ks * BK, (int)m0, a_full + 8 * sa);
-                if (++sa == SA) sa = 0, ph ^= 1;
-            }
-        }
-    } else if (warp == 2) {
-        if (lane == 0) {  // packed-weight producer: one stage = the 8 row tiles of this column tile
-            uint32_t sp = 0, ph = 1;
-            const uint8_t *src = p.tiles + rt0 * p.kt * (int64_t)F::TILE;
-            const int64_t row_stride = p.kt * (int64_t)F::TILE;
-            for (int kt = 0; kt < nkt; kt++) {
-                if (!mbar_wait(p_empty + 8 * sp, ph, p.status)) break;
-                mbar_expect_tx(p_full + 8 * sp, nrt * F::TILE);
-                for (int i = 0; i < nrt; i++)
-                    bulk_load(p_s + sp * P_BYTES + i * F::TILE, src + i * row_stride, F::TILE, p_full + 8 * sp);
-                src += F::TILE;
-                if (++sp == SP) sp = 0, ph ^= 1;
-            }
-        }
-    } else if (warp == 1) {
-        if (lane == 0) {
-            uint32_t sa = 0, pa = 0, sb = 0, pb = 0;
-            const uint64_t ad0 = umma_desc(a_s), bd0 = umma_desc(b_s);
-            for (int ks = 0; ks < nst; ks++) {
-                GEMM_TRACE(1, ks, 0);
-                if (!mbar_wait(a_full + 8 * sa, pa, p.status)) break;
-                GEMM_TRACE(1, ks, 1);
-                if (!mbar_wait(b_full + 8 * sb, pb, p.status)) break;
-                GEMM_TRACE(1, ks, 2);
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t ad = ad0 + ((sa * A_BYTES) >> 4), bd = bd0 + ((sb * B_BYTES) >> 4);
-#pragma unroll
-                for (int k = 0; k < BK / 16; k++)  // +32 bytes along K inside the 128-byte swizzle atom
-                    umma_bf16(tmem_d, ad + 2 * k, bd + 2 * k, (ks > 0 || k > 0) ? 1u : 0u);
-                umma_commit(a_empty + 8 * sa);
-                umma_commit(b_empty + 8 * sb);
-                GEMM_TRACE(1, ks, 3);
-                if (++sa == SA) sa = 0, pa ^= 1;
-                if (++sb == SB) sb = 0, pb ^= 1;
-            }
-            umma_commit(d_full);
-        }
-    } else {
-        // dequantize: thread = (weight row n of the tile, quarter qq of every 64-wide stage).  All four
-        // stages of a packed tile are converted into registers first, so the packed slot is released
-        // early and the wait for a free B stage does not delay the arithmetic.
-        const int dt = threadIdx.x - 32 * kFirstDequantWarp, n = dt & 127, qq = dt >> 7;
-        const int rtile = n >> 4, r = n & 15;
-        const bool row_exists = rtile < nrt;
-        bool ok = true;
-        uint32_t sp = 0, pp = 0, sb = 0, pb = 1;
-        const uint32_t row_off = n * 128, c0 = ((2 * qq) ^ (n & 7)) << 4, c1 = ((2 * qq + 1) ^ (n & 7)) << 4;
-        for (int kt = 0; kt < nkt && ok; kt++) {
-            ok = mbar_wait(p_full + 8 * sp, pp, p.status);
-            const uint32_t tile = p_s + sp * P_BYTES + rtile * F::TILE;
-            uint4 out[4][2];
-#pragma unroll
-            for (int q = 0; q < 4; q++) {
-#ifdef B200Q_GEMM_FAKE_DEQUANT
-                if (false) {
-#else
-                if (row_exists) {
-#endif
-                    dequant16<TYPE>(tile, r, 2 * q + (qq >> 1), qq & 1, out[q]);
-                } else {
-                    out[q][0] = out[q][1] = make_uint4(0u, 0u, 0u, 0u);
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(p_empty + 8 * sp);
-            if (++sp == SP) sp = 0, pp ^= 1;
-#pragma unroll
-            for (int q = 0; q < 4; q++) {
-                if (threadIdx.x == 32 * kFirstDequantWarp) GEMM_TRACE(2, kt * 4 + q, 0);
-                if (ok) ok = mbar_wait(b_empty + 8 * sb, pb, p.status);
-                if (threadIdx.x == 32 * kFirstDequantWarp) GEMM_TRACE(2, kt * 4 + q, 1);
-                const uint32_t rowbase = b_s + sb * B_BYTES + row_off;
-                sts128(rowbase + c0, out[q][0]);
-                sts128(rowbase + c1, out[q][1]);
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                if (threadIdx.x == 32 * kFirstDequantWarp) GEMM_TRACE(2, kt * 4 + q, 2);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(b_full + 8 * sb);
-                if (threadIdx.x == 32 * kFirstDequantWarp) GEMM_TRACE(2, kt * 4 + q, 3);
-                if (++sb == SB) sb = 0, pb ^= 1;
-            }
-        }
-        // epilogue: TMEM lane = batch row, column = weight row.  Warp w may read lanes 32*(w%4)..+31.
-        if (mbar_wait(d_full, 0, p.status)) {
-            if (threadIdx.x == 32 * kFirstDequantWarp) GEMM_TRACE(3, 0, 0);
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int quarter = warp & 3, colq = (warp - kFirstDequantWarp) >> 2;  // 16 warps: 4 lane quarters x 4 column quarters
-            const int64_t row = m0 + quarter * 32 + lane;
-            {
-                const int col0 = colq * 32;
-                uint32_t v[32];
-                tmem_ld32(tmem_d + ((uint32_t)(quarter * 32) << 16) + col0, v);
-                if (row < p.m) {
-                    const int64_t nbase = (int64_t)blockIdx.x * BN + col0;
-                    float *dst = p.y + row * p.y_ld + nbase;
-                    const bool vec = nbase + 32 <= p.n && (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
-                    if (vec) {  // 16-byte stores: a lane owns 32 consecutive outputs of one row
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 o;
-                            float *of = reinterpret_cast<float *>(&o);
-#pragma unroll
-                            for (int e = 0; e < 4; e++) {
-                                float f = __uint_as_float(v[j + e]);
-                                if (p.bias != nullptr) f += __ldg(p.bias + nbase + j + e);
-                                of[e] = apply_activation(p.act, f);
-                            }
-                            *reinterpret_cast<float4 *>(dst + j) = o;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            if (nbase + j < p.n) {
-                                float f = __uint_as_float(v[j]);
-                                if (p.bias != nullptr) f += __ldg(p.bias + nbase + j);
-                                dst[j] = apply_activation(p.act, f);
-                            }
-                        }
-                    }
-                }
-            }
-        }
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    GEMM_TRACE(3, 0, 1);
-    if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(BN) : "memory");
-    }
-}
-
 // ---------------------------------------------------------------------------------------
 // Kernel with the dequantized weights as the MMA's tensor-memory operand.
 //
@@ -508,13 +303,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p
 // ---------------------------------------------------------------------------------------
 constexpr int kTmemCols = 512;
 
-__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint4 &a, const uint4 &b) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(a.x), "r"(a.y),
                  "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
@@ -693,34 +481,39 @@ gemm_tmem_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            // MMA issuer.  Issuing an MMA blocks until the tensor pipe accepts it, and the pipe's queue is
-            // short, so the waits for the next stage are done while the current stage still has MMAs to
-            // issue: only the two commits separate the last MMA of a stage from the first of the next.
-            uint32_t st = 0, ph = 0;
-            const uint64_t xd0 = umma_desc(x_s);
-            bool ok = mbar_wait(full, 0, p.status);
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            uint32_t xlo = (uint32_t)xd0, alo = tmem_a;   // descriptor low word / operand address of the current stage
-            const uint32_t xhi = (uint32_t)(xd0 >> 32);
-            for (int ks = 0; ks < nst && ok; ks++) {
+        // MMA issuer.  The whole warp runs the loop, so that its bookkeeping is warp-uniform (the compiler
+        // can keep it on the uniform datapath, away from the ALU pipe the dequantize warps saturate); one
+        // lane issues.  Issuing an MMA blocks until the tensor pipe accepts it and the pipe's queue is
+        // short, so the wait for the next stage is done while the current stage still has an MMA to issue.
+        const bool leader = lane == 0;
+        uint32_t st = 0, ph = 0;
+        const uint64_t xd0 = umma_desc(x_s);
+        bool ok = mbar_wait(full, 0, p.status);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint32_t xlo = (uint32_t)xd0, alo = tmem_a;   // descriptor low word / operand address of the current stage
+        const uint32_t xhi = (uint32_t)(xd0 >> 32);
+        for (int ks = 0; ks < nst && ok; ks++) {
+            if (leader) {
                 GEMM_TRACE(1, ks, 0);
                 issue_mmas<R, BNB, 0, 3>(tmem_d, alo, xlo, xhi, IDESC, ks > 0 ? 1u : 0u);
                 GEMM_TRACE(1, ks, 1);
-                uint32_t nst_ = st + 1, nph = ph, nxlo = xlo + (X_BYTES >> 4), nalo = alo + C::A_COLS;
-                if (nst_ == S) nst_ = 0, nph ^= 1, nxlo = (uint32_t)xd0, nalo = tmem_a;
-                if (ks + 1 < nst) {
-                    ok = mbar_wait(full + 8 * nst_, nph, p.status);
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                }
+            }
+            uint32_t nst_ = st + 1, nph = ph, nxlo = xlo + (X_BYTES >> 4), nalo = alo + C::A_COLS;
+            if (nst_ == S) nst_ = 0, nph ^= 1, nxlo = (uint32_t)xd0, nalo = tmem_a;
+            if (ks + 1 < nst) {
+                ok = mbar_wait(full + 8 * nst_, nph, p.status);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            if (leader) {
                 GEMM_TRACE(1, ks, 2);
                 issue_mmas<R, BNB, 3, 4>(tmem_d, alo, xlo, xhi, IDESC, 1u);
                 umma_commit(empty + 8 * st);
                 GEMM_TRACE(1, ks, 3);
-                st = nst_, ph = nph, xlo = nxlo, alo = nalo;
             }
-            umma_commit(d_full);
+            st = nst_, ph = nph, xlo = nxlo, alo = nalo;
         }
+        if (leader) umma_commit(d_full);
+        __syncwarp();
     } else {
         // dequantize: warp = (TMEM lane quarter rb, share idx of each 64-wide stage).
         //   R = 2: idx = (row block h, 32-value half kh);  R = 1: idx = 16-value group
@@ -738,11 +531,7 @@ gemm_tmem_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
             for (int q = 0; q < 4; q++) {
                 if (threadIdx.x == 32 * kFirstDequantWarp) GEMM_TRACE(2, kt * 4 + q, 0);
                 uint4 out[4];
-#ifdef B200Q_GEMM_FAKE_DEQUANT
-                if (false) {
-#else
                 if (row_exists && ok) {
-#endif
                     if constexpr (R == 2) {
                         dequant32<TYPE>(tile, r, 2 * q + (idx & 1), out);
                     } else {
@@ -756,7 +545,6 @@ gemm_tmem_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
                 if (threadIdx.x == 32 * kFirstDequantWarp) GEMM_TRACE(2, kt * 4 + q, 1);
                 if (ok) ok = mbar_wait_relaxed(empty + 8 * sa, pa, p.status);
                 if (threadIdx.x == 32 * kFirstDequantWarp) GEMM_TRACE(2, kt * 4 + q, 2);
-#ifndef B200Q_GEMM_NO_ST
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 if constexpr (R == 2) {
                     tmem_st16(st_base + sa * C::A_COLS, out);
@@ -765,12 +553,9 @@ gemm_tmem_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-#endif
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full + 8 * sa);
                 if (threadIdx.x == 32 * kFirstDequantWarp) GEMM_TRACE(2, kt * 4 + q, 3);
-                if (lane == 0 && kt * 4 + q == 16) GEMM_TRACE(0, warp, 0);
-                if (lane == 0 && kt * 4 + q == 48) GEMM_TRACE(0, warp, 1);
                 if (++sa == S) sa = 0, pa ^= 1;
             }
             __syncwarp();
@@ -864,34 +649,16 @@ int launch_tmem(const Weight &w, const __nv_bfloat16 *x, int64_t m, const GemmPa
     return 0;
 }
 
-template <int TYPE>
-int launch_ss(const Weight &w, const __nv_bfloat16 *x, int64_t m, const GemmParams &p, cudaStream_t s) {
-    using F = Fmt<TYPE>;
-    CUtensorMap map;
-    int rc = encode_x_map(&map, x, m, w.k, BM);
-    if (rc != 0) return rc;
-    constexpr int SA = Depth<TYPE>::SA, SB = Depth<TYPE>::SB, SP = Depth<TYPE>::SP;
-    const size_t smem = 1024 + SA * BM * BK * 2 + SB * BN * BK * 2 + SP * 8 * F::TILE + 8 * (2 * SA + 2 * SB + 2 * SP + 1) + 16;
-    auto kern = gemm_tcgen05_kernel<TYPE>;
-    static thread_local bool configured[16] = {};
-    if (!configured[w.device & 15]) {
-        B200Q_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured[w.device & 15] = true;
-    }
-    dim3 grid((unsigned)((w.n + BN - 1) / BN), (unsigned)((m + BM - 1) / BM), 1);
-    kern<<<grid, kThreads, smem, s>>>(map, p);
-    return 0;
-}
-
-// Tile shape: 0 = shared-memory operand kernel, 1 = R1 x 128, 2 = R2 x 128, 3 = R1 x 256.
+// Tile shape: 1 = one row block x 128 batch rows, 2 = two row blocks x 128, 3 = one row block x 256.
+// B200Q_GEMM_SHAPE forces one (for measurements).
 int choose_shape(const Weight &w, int64_t m) {
     static const int forced = [] {
         const char *e = getenv("B200Q_GEMM_SHAPE");
-        return e != nullptr ? atoi(e) : -1;
+        return e != nullptr ? atoi(e) : 0;
     }();
-    if (forced >= 0) return forced;
+    if (forced >= 1 && forced <= 3) return forced;
     if (m > 128) return 3;
-    return (w.n + 127) / 128 > 2 * 148 ? 2 : 1;
+    return (w.n + 127) / 128 > 148 ? 2 : 1;   // more 128-row tiles than SMs: pair them up
 }
 
 template <int TYPE>
@@ -902,7 +669,6 @@ int launch_gemm_t(const Weight &w, const __nv_bfloat16 *x, int64_t m, const floa
     p.m = m, p.n = w.n, p.y_ld = y_ld, p.rt = w.rt, p.kt = w.kt, p.act = act;
     int rc;
     switch (choose_shape(w, m)) {
-    case 0: rc = launch_ss<TYPE>(w, x, m, p, s); break;
     case 1: rc = launch_tmem<TYPE, 1, 128>(w, x, m, p, s); break;
     case 2: rc = launch_tmem<TYPE, 2, 128>(w, x, m, p, s); break;
     default: rc = launch_tmem<TYPE, 1, 256>(w, x, m, p, s); break;

@@ -191,8 +191,6 @@ constexpr uint32_t H2_1024 = 0x64006400u;    // fp16x2 (1024, 1024)
 constexpr uint32_t H2_N1024 = 0xE400E400u;   // (-1024, -1024)
 constexpr uint32_t H2_N64 = 0xD400D400u;     // (-64, -64)
 constexpr uint32_t H2_1152 = 0x64806480u;    // (1152, 1152)
-constexpr uint32_t MAGIC_1024 = 0x64006400u; // exponent bits of 1024: low mantissa bits count 1
-constexpr uint32_t MAGIC_64 = 0x54005400u;   // exponent bits of 64: mantissa bit 4 counts 1
 constexpr uint32_t BYTES_64 = 0x64646464u;
 
 // Two bytes of `v` (selected by `sel`) as the fp16 pair (1024 + b_lo, 1024 + b_hi).
