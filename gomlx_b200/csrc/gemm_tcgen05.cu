@@ -67,6 +67,7 @@ struct GemmParams {
     int64_t m, n, y_ld;
     int64_t rt, kt;
     int act;
+    int splits;   // CTAs of a cluster (grid z) that share one output tile, each over 1/splits of K
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -296,10 +297,11 @@ __device__ __forceinline__ void dequant16(uint32_t tile, int r, int kq, int sub,
 // TMEM: R*BN accumulator columns (<= 256), then a ring of operand stages of 32*R columns each (one
 // 64-wide k stage of every row block) in the other 256 columns.
 //
-// TMEM lane L of a row block holds weight row 16*(L & 7) + (L >> 3) of the block: consecutive
-// lanes of a dequantize warp then read the same piece of 8 different row tiles, and with the row
-// tiles placed 16 bytes further apart than their size those 8 reads hit 8 different bank groups.
-// The epilogue reads D with lanes = weight rows and undoes the permutation when it stores.
+// TMEM lane L = 32*rb + lane of a row block holds row r = ((lane >> 2) & 7) + 8*(rb >> 1) of row tile
+// (lane & 3) + 4*(rb & 1).  The 8 lanes of a quarter warp then read the same piece of 4 row tiles x 2
+// adjacent rows, and with the row tiles placed 16 bytes further apart than their size those reads hit 8
+// different bank groups; in the epilogue (lanes = weight rows = columns of y) a warp instruction stores
+// 8 consecutive floats for each of 4 row tiles, i.e. whole 32-byte sectors.
 // ---------------------------------------------------------------------------------------
 constexpr int kTmemCols = 512;
 
@@ -410,9 +412,43 @@ template <int TYPE, int R, int BNB> struct TmemCfg {
     static constexpr size_t SMEM = 1024 + (size_t)S * X_BYTES + (size_t)SP * P_BYTES + 8 * NBAR + 16;
     static_assert(S >= 3, "stage ring too shallow");
     static_assert(R * BNB <= 256, "accumulators must fit in half of TMEM");
+    // a split-K peer parks its f32 accumulator (R*BNB columns x 128 lanes) in the rings after its main loop
+    static_assert((size_t)S * X_BYTES + (size_t)SP * P_BYTES >= (size_t)R * BNB * 128 * 4, "no room to park a partial tile");
 };
 
-template <int TYPE, int R, int BNB>
+// Split-K hand-over, kept out of line so that the register allocation of the main loop is the same
+// with and without it.  A partial tile is parked as [32-column part][column j][dequantize thread] f32.
+constexpr uint32_t kParkStride = kDequantWarps * 32 * 4;   // bytes between consecutive columns j
+__device__ __noinline__ void park_part(uint32_t taddr, uint32_t park) {
+    uint32_t v[32];
+    tmem_ld32(taddr, v);
+#pragma unroll
+    for (int j = 0; j < 32; j++) asm volatile("st.shared.u32 [%0], %1;" ::"r"(park + j * kParkStride), "r"(v[j]) : "memory");
+}
+// Rank 0: own accumulator + the parked partial sums of ranks 1 .. splits-1 (in rank order), then bias,
+// activation and the store of up to `rows` batch rows of one output column.
+__device__ __noinline__ void finish_part_split(uint32_t taddr, uint32_t park, int splits, float *dst, int64_t y_ld, int rows,
+                                               int act, float bias) {
+    uint32_t v[32];
+    tmem_ld32(taddr, v);
+    for (int sr = 1; sr < splits; sr++) {
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(park), "r"(sr));
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            float f;
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(f) : "r"(remote + j * kParkStride) : "memory");
+            v[j] = __float_as_uint(__uint_as_float(v[j]) + f);
+        }
+    }
+    if (dst != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 32; j++)
+            if (j < rows) dst[j * y_ld] = apply_activation(act, __uint_as_float(v[j]) + bias);
+    }
+}
+
+template <int TYPE, int R, int BNB, bool SPLITK>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tmem_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
     using F = Fmt<TYPE>;
@@ -437,7 +473,16 @@ gemm_tmem_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
     const int64_t m0 = (int64_t)blockIdx.y * BNB;
     const int64_t rt0 = (int64_t)blockIdx.x * RT;
     const int nrt = (int)min((int64_t)RT, p.rt - rt0);  // row tiles that exist in this CTA's rows
-    const int nkt = (int)p.kt, nst = nkt * 4;
+    // Split K: the CTAs of a cluster (grid z) take consecutive ranges of k tiles of the same output tile.
+    uint32_t split = 0;
+    int kt_begin = 0, nkt = (int)p.kt;
+    if constexpr (SPLITK) {
+        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(split));
+        const int kt_per = ((int)p.kt + p.splits - 1) / p.splits;
+        kt_begin = (int)split * kt_per;
+        nkt = max(min(kt_begin + kt_per, (int)p.kt) - kt_begin, 0);
+    }
+    const int nst = nkt * 4;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < S; i++) mbar_init(full + 8 * i, kDequantWarps + 1), mbar_init(empty + 8 * i, 1);
@@ -462,14 +507,14 @@ gemm_tmem_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
             for (int ks = 0; ks < nst; ks++) {
                 if (!mbar_wait_relaxed(empty + 8 * sx, ph, p.status)) break;
                 mbar_expect_tx(full + 8 * sx, X_BYTES);
-                tma_load_2d(x_s + sx * X_BYTES, &xmap, ks * BK, (int)m0, full + 8 * sx);
+                tma_load_2d(x_s + sx * X_BYTES, &xmap, (kt_begin * 4 + ks) * BK, (int)m0, full + 8 * sx);
                 if (++sx == S) sx = 0, ph ^= 1;
             }
         }
     } else if (warp == 2) {
         if (lane == 0) {  // packed-weight producer: one stage = one 256-value tile of every row tile
             uint32_t sp = 0, ph = 1;
-            const uint8_t *src = p.tiles + rt0 * p.kt * (int64_t)F::TILE;
+            const uint8_t *src = p.tiles + (rt0 * p.kt + kt_begin) * (int64_t)F::TILE;
             const int64_t row_stride = p.kt * (int64_t)F::TILE;
             for (int kt = 0; kt < nkt; kt++) {
                 if (!mbar_wait_relaxed(p_empty + 8 * sp, ph, p.status)) break;
@@ -519,7 +564,7 @@ gemm_tmem_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
         //   R = 2: idx = (row block h, 32-value half kh);  R = 1: idx = 16-value group
         const int rb = warp & 3, idx = (warp - kFirstDequantWarp) >> 2;
         const int h = R == 2 ? idx >> 1 : 0;
-        const int rtile = 8 * h + (lane & 7), r = 4 * rb + (lane >> 3);
+        const int tl = (lane & 3) + 4 * (rb & 1), rtile = 8 * h + tl, r = ((lane >> 2) & 7) + 8 * (rb >> 1);
         const bool row_exists = rtile < nrt;
         const uint32_t st_base = tmem_a + ((uint32_t)(32 * rb) << 16) + (R == 2 ? h * 32 + (idx & 1) * 16 : idx * 8);
         bool ok = true;
@@ -564,16 +609,37 @@ gemm_tmem_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
         }
         // epilogue: the R*BNB accumulator columns are split into four chunks, one per idx; a thread's TMEM
         // lane is one weight row (one column of y), its registers are consecutive batch rows.
-        if (mbar_wait(d_full, 0, p.status)) {
+        constexpr int CHUNK = R * BNB / 4;
+        const int c0 = idx * CHUNK;
+        const uint32_t park = x_s + (threadIdx.x - 32 * kFirstDequantWarp) * 4;  // [part][j][thread] f32
+        if (SPLITK && split != 0) {
+            // split-K peer: park the raw accumulator in this CTA's (now idle) rings for rank 0 to add
+            if (mbar_wait(d_full, 0, p.status)) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int part = 0; part < CHUNK / 32; part++)
+                    park_part(tmem_d + ((uint32_t)(32 * rb) << 16) + c0 + 32 * part, park + part * 32 * kParkStride);
+            }
+        }
+        if constexpr (SPLITK) {
+            __syncwarp();
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        }
+        if (split == 0 && mbar_wait(d_full, 0, p.status)) {
             if (threadIdx.x == 32 * kFirstDequantWarp) GEMM_TRACE(3, 0, 0);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            constexpr int CHUNK = R * BNB / 4;
-            const int c0 = idx * CHUNK, he = c0 / BNB, coff = c0 % BNB;
-            const int64_t col = (int64_t)blockIdx.x * (128 * R) + 128 * he + 16 * (lane & 7) + r;
+            const int he = c0 / BNB, coff = c0 % BNB;
+            const int64_t col = (int64_t)blockIdx.x * (128 * R) + 128 * he + 16 * tl + r;
             const bool col_ok = col < p.n;
             const float b = (p.bias != nullptr && col_ok) ? __ldg(p.bias + col) : 0.0f;
 #pragma unroll
             for (int part = 0; part < CHUNK / 32; part++) {
+                if constexpr (SPLITK) {
+                    const int64_t row0 = m0 + coff + 32 * part;
+                    finish_part_split(tmem_d + ((uint32_t)(32 * rb) << 16) + c0 + 32 * part, park + part * 32 * kParkStride, p.splits,
+                                      col_ok ? p.y + row0 * p.y_ld + col : nullptr, p.y_ld, (int)min((int64_t)32, p.m - row0), p.act, b);
+                    continue;
+                }
                 uint32_t v[32];
                 tmem_ld32(tmem_d + ((uint32_t)(32 * rb) << 16) + c0 + 32 * part, v);
                 if (col_ok) {
@@ -586,6 +652,16 @@ gemm_tmem_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p) {
                 }
             }
         }
+    }
+    if constexpr (SPLITK) {
+        __syncwarp();
+        if (warp < kFirstDequantWarp) {  // warps without an epilogue role join the hand-over barrier here
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        }
+        // second barrier: the parked partials stay alive until rank 0 has read them
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -633,19 +709,50 @@ int encode_x_map(CUtensorMap *map, const __nv_bfloat16 *x, int64_t m, int64_t k,
 }
 
 template <int TYPE, int R, int BNB>
-int launch_tmem(const Weight &w, const __nv_bfloat16 *x, int64_t m, const GemmParams &p, cudaStream_t s) {
+int launch_tmem(const Weight &w, const __nv_bfloat16 *x, int64_t m, const GemmParams &p0, cudaStream_t s) {
     using C = TmemCfg<TYPE, R, BNB>;
     CUtensorMap map;
     int rc = encode_x_map(&map, x, m, w.k, BNB);
     if (rc != 0) return rc;
-    auto kern = gemm_tmem_kernel<TYPE, R, BNB>;
     static thread_local bool configured[16] = {};
     if (!configured[w.device & 15]) {
-        B200Q_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+        B200Q_CUDA(cudaFuncSetAttribute(gemm_tmem_kernel<TYPE, R, BNB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+        B200Q_CUDA(cudaFuncSetAttribute(gemm_tmem_kernel<TYPE, R, BNB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
         configured[w.device & 15] = true;
     }
-    dim3 grid((unsigned)((w.n + 128 * R - 1) / (128 * R)), (unsigned)((m + BNB - 1) / BNB), 1);
-    kern<<<grid, kThreads, C::SMEM, s>>>(map, p);
+    GemmParams p = p0;
+    const unsigned gx = (unsigned)((w.n + 128 * R - 1) / (128 * R)), gy = (unsigned)((m + BNB - 1) / BNB);
+    // Too few output tiles for the GPU: 2 or 4 CTAs of a cluster share a tile, each over a part of K; rank 0
+    // adds the partial sums in rank order (deterministic) through distributed shared memory.
+    static const int forced = [] {
+        const char *e = getenv("B200Q_GEMM_SPLITS");
+        return e != nullptr ? atoi(e) : 0;
+    }();
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, w.device);
+    int splits = 1;
+    while (splits < 4 && (int64_t)gx * gy * splits * 2 <= sms && w.kt >= 4 * splits * 2) splits *= 2;
+    if (forced == 1 || forced == 2 || forced == 4) splits = forced;
+    while (splits > 1 && (int64_t)(splits - 1) * ((w.kt + splits - 1) / splits) >= w.kt) splits /= 2;  // no empty K range
+    p.splits = splits;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(gx, gy, (unsigned)splits);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::SMEM;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = (unsigned)splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = splits > 1 ? 1 : 0;
+    static const bool force_split_kernel = getenv("B200Q_GEMM_FORCE_SPLITK_KERNEL") != nullptr;
+    if (splits > 1 || force_split_kernel) {
+        B200Q_CUDA(cudaLaunchKernelEx(&cfg, gemm_tmem_kernel<TYPE, R, BNB, true>, map, p));
+    } else {
+        B200Q_CUDA(cudaLaunchKernelEx(&cfg, gemm_tmem_kernel<TYPE, R, BNB, false>, map, p));
+    }
     return 0;
 }
 

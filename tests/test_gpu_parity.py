@@ -183,6 +183,41 @@ def test_gemm_ragged_k(oracle, name):
     assert rel_err(y.cpu().numpy(), ref) <= TOL_GEMM
 
 
+@pytest.mark.parametrize("name", ["Q4_K", "Q6_K", "Q8_0", "Q4_0"])
+def test_gemm_paired_row_blocks(oracle, name):
+    """m <= 128 with more 128-row tiles than SMs: the tile shape with two row blocks per CTA; N is not a
+    multiple of 256, so the last CTA has an empty second block and a ragged first one."""
+    t = TYPES[name]
+    m, n, k = 96, 148 * 128 + 128 + 40, 512
+    w = oracle.make_weights(int(t), n, k, seed=9)
+    rng = np.random.default_rng(17)
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    bias = rng.standard_normal(n).astype(np.float32)
+    ref = oracle.dense(int(t), w, x.float().cpu().numpy(), bias, 0, route="f64")
+    y = g.quantized_dense(x, w, quant(t), torch.from_numpy(bias).cuda())
+    assert g.last_kernel() == nat.KERNEL_GEMM_TCGEN05
+    assert rel_err(y.cpu().numpy(), ref) <= TOL_GEMM
+
+
+@pytest.mark.parametrize("name,m,n,k", [("Q4_K", 100, 200, 4096), ("Q8_0", 300, 256, 2048), ("Q6_K", 33, 48, 8192),
+                                         ("Q4_0", 512, 1000, 1280)])
+def test_gemm_split_k(oracle, name, m, n, k):
+    """Few output tiles and a long K: the CTAs of a cluster share a tile, each over a part of K."""
+    t = TYPES[name]
+    w = oracle.make_weights(int(t), n, k, seed=21)
+    rng = np.random.default_rng(k + m)
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    bias = rng.standard_normal(n).astype(np.float32)
+    ref = oracle.dense(int(t), w, x.float().cpu().numpy(), bias, 0, route="f64")
+    wr = g.upload(w, t)
+    y = g.quantized_dense(x, wr, quant(t), torch.from_numpy(bias).cuda())
+    assert g.last_kernel() == nat.KERNEL_GEMM_TCGEN05
+    assert nat.lib().b200q_weight_check(wr.handle, None) == 0
+    assert rel_err(y.cpu().numpy(), ref) <= TOL_GEMM
+    assert torch.equal(y, g.quantized_dense(x, wr, quant(t), torch.from_numpy(bias).cuda()))
+    wr.free()
+
+
 def test_gemm_prefill_config_shapes(oracle):
     """configs[2]: Q4_K, x bf16 [512, 4096], W 4096 x 4096 (oracle on all rows) and 4096 x 14336 (sampled rows)."""
     t = g.GGMLQuantType.Q4_K
