@@ -434,12 +434,11 @@ __device__ __noinline__ void finish_part_split(uint32_t taddr, uint32_t park, in
     for (int sr = 1; sr < splits; sr++) {
         uint32_t remote;
         asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(park), "r"(sr));
+        float f[32];  // all loads first: their latencies overlap
 #pragma unroll
-        for (int j = 0; j < 32; j++) {
-            float f;
-            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(f) : "r"(remote + j * kParkStride) : "memory");
-            v[j] = __float_as_uint(__uint_as_float(v[j]) + f);
-        }
+        for (int j = 0; j < 32; j++) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(f[j]) : "r"(remote + j * kParkStride));
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + f[j]);
     }
     if (dst != nullptr) {
 #pragma unroll

@@ -657,28 +657,41 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
     __syncwarp();
 
     // Producer (lane 0 of each warp): walks the same (unit, k tile) sequence as the consumer,
-    // `depth` slots ahead.  Unit u = row * kp + part; (prow, ppart) track it without divisions.
+    // `depth` slots ahead.  Unit u = row * kp + part; (prow, ppart) track it without divisions.  Inside a
+    // unit only a source pointer and a tile count advance, so that issuing a slot costs a handful of
+    // instructions; the unit bookkeeping runs once per unit.
     int prow = 0, ppart = warp, pd = 0;
     while (ppart >= p.kp) ppart -= p.kp, prow++;
-    int pk = kt_begin + ppart * p.ktp, pk1 = min(pk + p.ktp, kt_end);
-    auto producer_skip_empty = [&]() {
-        while (prow < nrows && pk >= pk1) {
+    const uint8_t *psrc = nullptr;  // next tile of the producer's current unit
+    int pleft = 0;                  // tiles left in it
+    auto producer_enter_unit = [&]() {  // skips empty units; leaves prow == nrows when the work is exhausted
+        while (prow < nrows) {
+            const int pk = kt_begin + ppart * p.ktp, pk1 = min(pk + p.ktp, kt_end);
+            if (pk < pk1) {
+                const Segment &sg = p.seg[segment_of(p, r0 + prow)];
+                psrc = sg.tiles + ((int64_t)(r0 + prow - sg.rt0) * p.kt + pk) * (int64_t)F::TILE;
+                pleft = pk1 - pk;
+                return;
+            }
             ppart += nwarps;
             while (ppart >= p.kp) ppart -= p.kp, prow++;
-            pk = kt_begin + ppart * p.ktp, pk1 = min(pk + p.ktp, kt_end);
         }
     };
     if (nunits == 0) prow = nrows;
-    producer_skip_empty();
+    producer_enter_unit();
     auto issue_next = [&]() {
-        const int nt = min(p.tps, pk1 - pk);
-        const Segment &sg = p.seg[segment_of(p, r0 + prow)];
-        const uint8_t *src = sg.tiles + ((int64_t)(r0 + prow - sg.rt0) * p.kt + pk) * (int64_t)F::TILE;
-        mbar_expect_tx(bars_s + 8 * pd, nt * F::TILE);
-        bulk_load(ring_s + pd * slot_bytes, src, nt * F::TILE, bars_s + 8 * pd);
+        const int nt = min(p.tps, pleft);
+        const uint32_t bytes = nt * F::TILE;
+        mbar_expect_tx(bars_s + 8 * pd, bytes);
+        bulk_load(ring_s + pd * slot_bytes, psrc, bytes, bars_s + 8 * pd);
         if (++pd == p.depth) pd = 0;
-        pk += nt;
-        producer_skip_empty();
+        psrc += bytes;
+        pleft -= nt;
+        if (pleft == 0) {
+            ppart += nwarps;
+            while (ppart >= p.kp) ppart -= p.kp, prow++;
+            producer_enter_unit();
+        }
     };
     B200Q_TRACE_POINT(6);
     // `pre_issue` slots are requested before the activations are staged, the rest right after.
@@ -733,7 +746,7 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
     B200Q_TRACE_POINT(1);
 
     int cd = 0;
-    uint32_t cphase = 0;
+    uint32_t cphase = 0, cslot = ring_s;  // consumer's ring slot: index, phase bit, shared-memory address
     bool timed_out = false;
     int crow = 0, cpart = warp;
     while (cpart >= p.kp) cpart -= p.kp, crow++;
@@ -746,17 +759,17 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
 #pragma unroll
                 for (int i = 0; i < 4; i++) acc[a][nb][i] = 0.0f;
         const int k0 = kt_begin + cpart * p.ktp, k1 = min(k0 + p.ktp, kt_end);
-        for (int kt = k0; kt < k1;) {
-            const int nt = min(p.tps, k1 - kt);
+        // The activation addresses of the unit's first tile; every further tile is a constant step on.
+        XCols<NB> xc;
+        xcols_for_tile<NB>(xc, xb, (k0 - kt_begin) * 32, F::SUB ? (k0 - kt_begin) * (F::TK / F::SUB) : 0, swz_a, swz_b);
+        for (int left = k1 - k0; left > 0;) {
+            const int nt = min(p.tps, left);
             if (!mbar_wait(bars_s + 8 * cd, cphase)) timed_out = true;
 #ifdef B200Q_TRACE
-            if (crow == 0 && kt == k0) B200Q_TRACE_POINT(2);
+            if (crow == 0 && left == k1 - k0) B200Q_TRACE_POINT(2);
 #endif
+            uint32_t tile = cslot;
             for (int ti = 0; ti < nt; ti++) {
-                const uint32_t tile = ring_s + cd * slot_bytes + ti * F::TILE;
-                const int kl = kt + ti - kt_begin;  // tile index inside the staged slice
-                XCols<NB> xc;
-                xcols_for_tile<NB>(xc, xb, kl * 32, F::SUB ? kl * (F::TK / F::SUB) : 0, swz_a, swz_b);
                 if constexpr (TYPE == kQ4_0) {
                     tile_q4_0<NB>(tile, lane, xc, nc, acc);
                 } else if constexpr (TYPE == kQ8_0) {
@@ -766,9 +779,17 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
                 } else {
                     tile_q6_k<NB>(tile, lane, xc, acc);
                 }
+                tile += F::TILE;
+#pragma unroll
+                for (int nb = 0; nb < NB; nb++) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) xc.r[nb][i] += 32 * 16;
+                    if constexpr (F::SUB != 0) xc.shi[nb] += (F::TK / F::SUB) * 2, xc.slo[nb] += (F::TK / F::SUB) * 2;
+                }
             }
-            kt += nt;
-            if (++cd == p.depth) cd = 0, cphase ^= 1;
+            left -= nt;
+            cslot += slot_bytes;
+            if (++cd == p.depth) cd = 0, cphase ^= 1, cslot = ring_s;
             __syncwarp();  // all lanes have read the slot
             if (lane == 0 && prow < nrows) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
