@@ -200,7 +200,7 @@ def run_cuda(args) -> None:
     peer_layers = None
     if gather == "peer":
         try:
-            from gomlx_b200.sharded import PeerScatterBuffers, PeerScatterDense
+            from gomlx_b200.sharded import PeerScatterBuffers, PeerScatterDense, peer_scatter_batch
             per_layer = sum(n for _, _, n, _, _ in PROJECTIONS) * batch
             bufs = PeerScatterBuffers(LAYERS * per_layer, local)
             peer_layers, off = [], 0
@@ -234,13 +234,21 @@ def run_cuda(args) -> None:
         pending = False  # a signal has been published that the next launch has to wait for
         for li in range(LAYERS):
             for pi, (name, t, _, k, act) in enumerate(PROJECTIONS):
-                if gather == "peer" and args.order == "kernel":
-                    sig = name in sync_after
-                    peer_layers[li][pi](x_dev[k], None, act_types[act], wait=pending, signal=sig)
+                if gather == "peer" and args.fuse_shared_input and name in ("k", "up"):
+                    continue  # computed together with q / gate
+                if gather == "peer":
+                    sig = args.order == "kernel" and name in sync_after
+                    if args.fuse_shared_input and name in ("q", "gate"):  # q+k, gate+up: one launch each
+                        peer_scatter_batch([peer_layers[li][pi], peer_layers[li][pi + 1]], x_dev[k], None,
+                                           [act_types[act], act_types[PROJECTIONS[pi + 1][4]]],
+                                           wait=pending, signal=sig or (args.order == "kernel" and PROJECTIONS[pi + 1][0] in sync_after))
+                        sig = sig or (args.order == "kernel" and PROJECTIONS[pi + 1][0] in sync_after)
+                        last = PROJECTIONS[pi + 1][0]
+                    else:
+                        peer_layers[li][pi](x_dev[k], None, act_types[act], wait=pending, signal=sig)
+                        last = name
                     pending = sig
-                elif gather == "peer":
-                    peer_layers[li][pi](x_dev[k], None, act_types[act])
-                    if name in sync_after:
+                    if args.order == "barrier" and last in sync_after:
                         bufs.barrier()
                 elif gather == "nccl":
                     g.backend_fused_quantized_dense(x_dev[k], weights[li][pi], None, quant[t], acts[act], out=y_loc[li][pi])
@@ -362,12 +370,12 @@ def run_cuda(args) -> None:
                    "inputs": "fixed N(0,1) activations per projection (outputs not chained)",
                    "l2": f"no flush: {local_bytes / 1e6:.0f} MB of weights per GPU per step exceed the 126 MB L2",
                    "launch": ("one CUDA graph per step; q+k and gate+up of a layer share one launch each (160 launches)"
-                              if (world == 1 and args.fuse_shared_input) else "one CUDA graph of 224 GEMV launches per step")},
+                              if (args.fuse_shared_input and gather in ("none", "peer")) else "one CUDA graph of 224 GEMV launches per step")},
         "roofline": roofline,
         "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": int(sum(v.numel() * 4 for v in x_host.values())),
                 "d2h_bytes_per_step": int(y_host.numel() * 4)},
-        "gpu_launches": int(args.steps * LAYERS * (5 if (world == 1 and args.fuse_shared_input) else len(PROJECTIONS))),
+        "gpu_launches": int(args.steps * LAYERS * (5 if (args.fuse_shared_input and gather in ("none", "peer")) else len(PROJECTIONS))),
         "clocks": clk,
     }
     if rank == 0:

@@ -261,25 +261,59 @@ int b200q_dense_batch(int count, const b200q_weight_t *hs, const void *x_dev, in
                              static_cast<cudaStream_t>(stream));
 }
 
+int b200q_dense_batch_scatter(int count, const b200q_weight_t *hs, const void *x_dev, int x_dtype, int64_t m,
+                              const float *const *biases_dev, const int *activations, float *const *y_locals,
+                              float *const *y_peers, int n_peers, const int64_t *y_lds, const int64_t *row_offsets,
+                              int *sync_local, int *const *sync_peers, int rank, int sync_flags, void *stream) {
+    if (count < 1 || count > 4 || !hs || !y_locals || !activations || !y_lds || !row_offsets)
+        return fail(B200Q_EINVAL, "dense_batch_scatter: 1..4 matrices with outputs, leading dimensions and row offsets");
+    if (m == 0) return B200Q_OK;
+    if (m < 0 || m > 16) return fail(B200Q_ENOTIMPL, "dense_batch_scatter: only the decode path (m <= 16) scatters to peers");
+    if (!x_dev) return fail(B200Q_EINVAL, "dense_batch_scatter: null x");
+    if (x_dtype != B200Q_F32 && x_dtype != B200Q_BF16) return fail(B200Q_EINVAL, "dense_batch_scatter: x dtype must be f32 or bf16");
+    if (n_peers < 0 || n_peers > 7 || (n_peers > 0 && !y_peers)) return fail(B200Q_EINVAL, "dense_batch_scatter: at most 7 peers");
+    if (sync_flags != 0 && (sync_local == nullptr || (n_peers > 0 && sync_peers == nullptr) || rank < 0 || rank > n_peers))
+        return fail(B200Q_EINVAL, "dense_batch_scatter: sync flags need the sync words of every rank and a valid rank");
+    if (reinterpret_cast<uintptr_t>(x_dev) & 15) return fail(B200Q_EINVAL, "dense_batch_scatter: x must be 16-byte aligned");
+    std::vector<std::shared_ptr<Weight>> ws((size_t)count);
+    const Weight *wp[4];
+    float *ys[4];
+    int64_t deltas[7] = {};
+    for (int i = 0; i < count; i++) {
+        ws[i] = find(hs[i]);
+        if (!ws[i]) return fail(B200Q_EHANDLE, "dense_batch_scatter: unknown handle");
+        wp[i] = ws[i].get();
+        if (!y_locals[i]) return fail(B200Q_EINVAL, "dense_batch_scatter: null y");
+        if (activations[i] < B200Q_ACT_NONE || activations[i] > B200Q_ACT_TANH) return fail(B200Q_EINVAL, "dense_batch_scatter: bad activation");
+        if (row_offsets[i] < 0 || y_lds[i] < row_offsets[i] + ws[i]->n)
+            return fail(B200Q_EINVAL, "dense_batch_scatter: y_ld smaller than row_offset + N");
+        if (ws[i]->type != ws[0]->type || ws[i]->k != ws[0]->k || ws[i]->device != ws[0]->device)
+            return fail(B200Q_EINVAL, "dense_batch_scatter: matrices of one launch must share format, K and device");
+        ys[i] = y_locals[i] + row_offsets[i];
+        // every output of the launch must sit at the same distance from its copy on a given peer
+        for (int r = 0; r < n_peers; r++) {
+            float *peer = y_peers[(size_t)i * n_peers + r];
+            if (!peer) return fail(B200Q_EINVAL, "dense_batch_scatter: null peer pointer");
+            const int64_t d = reinterpret_cast<intptr_t>(peer) - reinterpret_cast<intptr_t>(y_locals[i]);
+            if (i == 0) deltas[r] = d;
+            else if (deltas[r] != d)
+                return fail(B200Q_EINVAL, "dense_batch_scatter: the outputs of one launch must lie in one peer-mapped buffer per GPU");
+        }
+    }
+    B200Q_CUDA(cudaSetDevice(ws[0]->device));
+    g_last_kernel = B200Q_KERNEL_GEMV_MMA;
+    return launch_gemv_batch(count, wp, x_dev, x_dtype, (int)m, biases_dev, activations, ys, y_lds, static_cast<cudaStream_t>(stream),
+                             deltas, n_peers, sync_local, sync_peers, rank, sync_flags);
+}
+
 int b200q_dense_scatter(b200q_weight_t h, const void *x_dev, int x_dtype, int64_t m, const float *bias_dev, int activation,
                         float *y_local, float *const *y_peers, int n_peers, int64_t y_ld, int64_t row_offset,
                         int *sync_local, int *const *sync_peers, int rank, int sync_flags, void *stream) {
-    auto w = find(h);
-    if (!w) return fail(B200Q_EHANDLE, "dense_scatter: unknown handle");
-    if (m == 0) return B200Q_OK;
-    if (m < 0 || m > 16) return fail(B200Q_ENOTIMPL, "dense_scatter: only the decode path (m <= 16) scatters to peers");
-    if (!x_dev || !y_local) return fail(B200Q_EINVAL, "dense_scatter: null x or y");
-    if (x_dtype != B200Q_F32 && x_dtype != B200Q_BF16) return fail(B200Q_EINVAL, "dense_scatter: x dtype must be f32 or bf16");
-    if (activation < B200Q_ACT_NONE || activation > B200Q_ACT_TANH) return fail(B200Q_EINVAL, "dense_scatter: bad activation");
-    if (n_peers < 0 || n_peers > 7) return fail(B200Q_EINVAL, "dense_scatter: at most 7 peers");
-    if (sync_flags != 0 && (sync_local == nullptr || (n_peers > 0 && sync_peers == nullptr) || rank < 0 || rank > n_peers))
-        return fail(B200Q_EINVAL, "dense_scatter: sync flags need the sync words of every rank and a valid rank");
-    if (row_offset < 0 || y_ld < row_offset + w->n) return fail(B200Q_EINVAL, "dense_scatter: y_ld smaller than row_offset + N");
-    if (reinterpret_cast<uintptr_t>(x_dev) & 15) return fail(B200Q_EINVAL, "dense_scatter: x must be 16-byte aligned");
-    B200Q_CUDA(cudaSetDevice(w->device));
-    g_last_kernel = B200Q_KERNEL_GEMV_MMA;
-    return launch_gemv(*w, x_dev, x_dtype, (int)m, bias_dev, activation, y_local, y_ld, static_cast<cudaStream_t>(stream),
-                       y_peers, n_peers, row_offset, sync_local, sync_peers, rank, sync_flags);
+    if (!y_local) return fail(B200Q_EINVAL, "dense_scatter: null x or y");
+    const float *biases[1] = {bias_dev};
+    float *ys[1] = {y_local};
+    return b200q_dense_batch_scatter(1, &h, x_dev, x_dtype, m, biases, &activation, ys, y_peers, n_peers, &y_ld, &row_offset,
+                                     sync_local, sync_peers, rank, sync_flags, stream);
 }
 
 int b200q_dense_f32_prefill_noalloc(b200q_weight_t h, const float *x_dev, int64_t m, const float *bias_dev,

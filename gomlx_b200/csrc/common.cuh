@@ -40,12 +40,13 @@ int launch_gather(const Weight &w, const int32_t *idx, int64_t n_idx, float *out
 
 // gemv_mma.cu
 int launch_gemv(const Weight &w, const void *x, int x_dtype, int m, const float *bias, int act, float *y, int64_t y_ld,
-                cudaStream_t s, float *const *y_peers = nullptr, int npeers = 0, int64_t row_off = 0,
-                int *sync_local = nullptr, int *const *sync_peers = nullptr, int rank = 0, int sync_flags = 0);
+                cudaStream_t s);
 
+// Up to 4 matrices of one format and K on the same activations in one launch.  y_peer_deltas[r]: byte distance
+// from every local output element to its copy on peer r (row-sharded layers, all outputs in one symmetric buffer).
 int launch_gemv_batch(int count, const Weight *const *ws, const void *x, int x_dtype, int m, const float *const *biases,
                       const int *acts, float *const *ys, const int64_t *y_lds, cudaStream_t s,
-                      float *const *y_peers = nullptr, int npeers = 0, int64_t row_off = 0, int *sync_local = nullptr,
+                      const int64_t *y_peer_deltas = nullptr, int npeers = 0, int *sync_local = nullptr,
                       int *const *sync_peers = nullptr, int rank = 0, int sync_flags = 0);
 
 // gemm_tcgen05.cu

@@ -71,8 +71,10 @@ struct GemvParams {
     Segment seg[kMaxSegments];
     int nseg;
     const void *x;
-    float *y_peer[7];  // the same output buffer on the other GPUs of a row-sharded layer (NVLink peer memory)
-    int npeers;        // number of valid entries in y_peer
+    // Row-sharded layers: every output buffer of the launch exists at the same offset of one peer-mapped
+    // (symmetric) buffer per GPU, so peer r's copy of an element lies y_peer_delta[r] bytes from the local one.
+    int64_t y_peer_delta[7];
+    int npeers;        // number of valid entries in y_peer_delta
     // Cross-GPU ordering without extra launches.  Each rank owns a small word array in peer-mapped memory:
     // [r] = number of "signal" kernels rank r has completed (written by rank r), [8] = this rank's own
     // count, [9] = CTAs of the running kernel that have finished.  A kernel launched with kSyncSignal
@@ -83,7 +85,6 @@ struct GemvParams {
     int rank, sync_flags;
     int *status;
     int64_t k;
-    int64_t row_off;   // first output column of this shard inside the full [m, N_total] result
     int64_t rt, kt;  // row tiles (16 rows) and k tiles (256 values) of the weight
     int m, x_dtype;
     int splits;     // CTAs per cluster (power of two); split s owns k tiles [s*kts, (s+1)*kts)
@@ -839,9 +840,10 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
             // buffer of every peer GPU (plain stores over NVLink): the all-gather of the outputs happens
             // in the epilogue, tile by tile, instead of in a collective after the kernel.
             const float out = apply_activation(sg.act, v);
-            const int64_t at = (int64_t)col * sg.y_ld + p.row_off + row;
-            sg.y[at] = out;
-            for (int pr = 0; pr < p.npeers; pr++) p.y_peer[pr][at] = out;
+            float *dst = sg.y + (int64_t)col * sg.y_ld + row;  // sg.y already points at this shard's first column
+            *dst = out;
+            for (int pr = 0; pr < p.npeers; pr++)
+                *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + p.y_peer_delta[pr]) = out;
         }
     }
     if (p.splits > 1) cluster.sync();  // keep shared memory alive until every peer has read it
@@ -1008,12 +1010,11 @@ int launch_nb(const Weight &w, const GemvParams &p, cudaStream_t s) {
 }  // namespace
 
 int launch_gemv_batch(int count, const Weight *const *ws, const void *x, int x_dtype, int m, const float *const *biases,
-                      const int *acts, float *const *ys, const int64_t *y_lds, cudaStream_t s, float *const *y_peers,
-                      int npeers, int64_t row_off, int *sync_local, int *const *sync_peers, int rank, int sync_flags) {
+                      const int *acts, float *const *ys, const int64_t *y_lds, cudaStream_t s, const int64_t *y_peer_deltas,
+                      int npeers, int *sync_local, int *const *sync_peers, int rank, int sync_flags) {
     if (m < 1 || m > 16) return fail(B200Q_EINVAL, "gemv: m must be in 1..16");
     if (count < 1 || count > kMaxSegments) return fail(B200Q_EINVAL, "gemv: 1..4 matrices per launch");
-    if (npeers < 0 || npeers > 7 || (npeers > 0 && (y_peers == nullptr || count != 1)))
-        return fail(B200Q_EINVAL, "gemv: bad peer list");
+    if (npeers < 0 || npeers > 7 || (npeers > 0 && y_peer_deltas == nullptr)) return fail(B200Q_EINVAL, "gemv: bad peer list");
     GemvParams p{};
     Weight all = *ws[0];  // launch-wide view: same format, K and device, row tiles numbered through
     int64_t rt = 0;
@@ -1028,9 +1029,8 @@ int launch_gemv_batch(int count, const Weight *const *ws, const void *x, int x_d
     p.nseg = count;
     all.rt = rt;
     p.x = x;
-    for (int i = 0; i < npeers; i++) p.y_peer[i] = y_peers[i];
+    for (int i = 0; i < npeers; i++) p.y_peer_delta[i] = y_peer_deltas[i];
     p.npeers = npeers;
-    p.row_off = row_off;
     p.sync_local = sync_local;
     for (int i = 0; i < npeers && sync_peers != nullptr; i++) p.sync_peer[i] = sync_peers[i];
     p.rank = rank, p.sync_flags = (sync_local != nullptr && (npeers == 0 || sync_peers != nullptr)) ? sync_flags : 0;
@@ -1048,13 +1048,11 @@ int launch_gemv_batch(int count, const Weight *const *ws, const void *x, int x_d
 }
 
 int launch_gemv(const Weight &w, const void *x, int x_dtype, int m, const float *bias, int act, float *y, int64_t y_ld,
-                cudaStream_t s, float *const *y_peers, int npeers, int64_t row_off, int *sync_local, int *const *sync_peers,
-                int rank, int sync_flags) {
+                cudaStream_t s) {
     const Weight *ws[1] = {&w};
     const float *biases[1] = {bias};
     float *ys[1] = {y};
-    return launch_gemv_batch(1, ws, x, x_dtype, m, biases, &act, ys, &y_ld, s, y_peers, npeers, row_off, sync_local,
-                             sync_peers, rank, sync_flags);
+    return launch_gemv_batch(1, ws, x, x_dtype, m, biases, &act, ys, &y_ld, s, nullptr, 0, nullptr, nullptr, 0, 0);
 }
 
 }  // namespace b200q

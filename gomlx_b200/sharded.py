@@ -11,7 +11,7 @@ the CPU tests, where ``compute`` is injected because the CUDA library cannot run
 """
 from __future__ import annotations
 
-from typing import Callable, Optional
+from typing import Callable, Optional, Sequence
 
 import torch
 import torch.distributed as dist
@@ -157,3 +157,37 @@ class PeerScatterDense:
 
     def free(self) -> None:
         self.local.free()
+
+
+def peer_scatter_batch(layers: Sequence["PeerScatterDense"], x: torch.Tensor, biases=None, activations=None,
+                       wait: bool = False, signal: bool = False):
+    """Several row-sharded projections on the same ``x`` in one launch (``b200q_dense_batch_scatter``): q+k or
+    gate+up of a decoder layer.  The layers must share one ``PeerScatterBuffers``, format and K.  Returns the
+    list of gathered result views (valid on every rank after the next ``buffers.barrier()``)."""
+    import ctypes
+    from . import _native as nat
+    first = layers[0]
+    bufs, n = first.buffers, len(layers)
+    if any(l.buffers is not bufs for l in layers):
+        raise ValueError("peer_scatter_batch: the layers must share one PeerScatterBuffers")
+    x2 = x.reshape(-1, first.local.k).contiguous()
+    m = x2.shape[0]
+    if any(m > l.max_m for l in layers):
+        raise ValueError(f"batch {m} exceeds the rows reserved for a layer")
+    acts = list(activations) if activations is not None else [Activation.NONE] * n
+    bs = []
+    for l, b in zip(layers, biases if biases is not None else [None] * n):
+        bs.append(None if b is None else b[l.local.row_begin:l.local.row_begin + l.local.n].contiguous())
+    peers_of = [r for r in range(bufs.world) if r != bufs.rank]
+    handles = (ctypes.c_uint64 * n)(*[l.local.handle for l in layers])
+    bias_arr = (ctypes.c_void_p * n)(*[b.data_ptr() if b is not None else None for b in bs])
+    act_arr = (ctypes.c_int * n)(*[int(a.to_backend()) for a in acts])
+    y_loc = (ctypes.c_void_p * n)(*[bufs.ptr(bufs.rank, l.offset) for l in layers])
+    y_peer = (ctypes.c_void_p * max(1, n * len(peers_of)))(*[bufs.ptr(r, l.offset) for l in layers for r in peers_of])
+    lds = (ctypes.c_int64 * n)(*[l.n_total for l in layers])
+    offs = (ctypes.c_int64 * n)(*[l.local.row_begin for l in layers])
+    nat.check(nat.lib().b200q_dense_batch_scatter(
+        n, handles, ctypes.c_void_p(x2.data_ptr()), nat.F32 if x2.dtype == torch.float32 else nat.BF16, m, bias_arr, act_arr,
+        y_loc, y_peer, len(peers_of), lds, offs, ctypes.c_void_p(bufs.sync_ptr(bufs.rank)), first._sync_arr, bufs.rank,
+        (1 if wait else 0) | (2 if signal else 0), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    return [l.y[:m] for l in layers]

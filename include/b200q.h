@@ -154,6 +154,17 @@ int b200q_dense_scatter(b200q_weight_t w, const void *x_dev, int x_dtype, int64_
                         float *y_local, float *const *y_peers, int n_peers, int64_t y_ld, int64_t row_offset,
                         int *sync_local, int *const *sync_peers, int rank, int sync_flags, void *stream);
 
+/* b200q_dense_scatter for up to 4 row shards that read the same activations (q+k, gate+up of a decoder layer:
+ * the caller in ml/zoo/transformer/transformer.go:1049-1054,1286-1294 applies them to one x): one launch.
+ * Arrays have `count` entries; y_peers is [count][n_peers] flattened (matrix i, peer r at i*n_peers + r) and
+ * every matrix' outputs must lie in the same peer-mapped buffer per GPU, i.e. y_peers[i][r] - y_locals[i] must
+ * not depend on i (true for regions of one symmetric allocation); otherwise B200Q_EINVAL.  The matrices must
+ * share format, K and device.  Sync words and flags as for b200q_dense_scatter. */
+int b200q_dense_batch_scatter(int count, const b200q_weight_t *shards, const void *x_dev, int x_dtype, int64_t m,
+                              const float *const *biases_dev, const int *activations, float *const *y_locals,
+                              float *const *y_peers, int n_peers, const int64_t *y_lds, const int64_t *row_offsets,
+                              int *sync_local, int *const *sync_peers, int rank, int sync_flags, void *stream);
+
 /* No counterpart in the reference: an allocation-free form of b200q_dense for prefill (m > 16) with f32
  * activations.  b200q_dense converts f32 activations to bf16 in a buffer it takes from the CUDA
  * stream-ordered allocator; callers that must not allocate at that point (a serving loop inside an

@@ -27,7 +27,7 @@ def _worker(rank, world, port, q):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         import gomlx_b200 as g
-        from gomlx_b200.sharded import PeerScatterBuffers, PeerScatterDense
+        from gomlx_b200.sharded import PeerScatterBuffers, PeerScatterDense, peer_scatter_batch
         from oracle import oracle as o
         n, k, max_m = 1024 + 48, 2048, 8
         quant = g.Quantization(g.QuantizationScheme.GGML, g.GGMLQuantType.Q4_K)
@@ -46,6 +46,22 @@ def _worker(rank, world, port, q):
             err = np.abs(y.cpu().numpy() - ref).max() / np.abs(pre).max()
             assert err <= 3e-3, (rank, m, err)
             bufs.barrier()  # nobody overwrites the buffers while a peer still reads them
+        # two projections on the same activations in one launch (q+k / gate+up), regions of one buffer
+        n2 = 512 + 16
+        w2 = o.make_weights(o.Q4_K, n2, k, seed=3)
+        bufs2 = PeerScatterBuffers(max_m * (n + n2), rank)
+        la = PeerScatterDense(w, quant, bufs2, 0, max_m, rank)
+        lb = PeerScatterDense(w2, quant, bufs2, max_m * n, max_m, rank)
+        x = rng.standard_normal((3, k)).astype(np.float32)
+        ya, yb = peer_scatter_batch([la, lb], torch.from_numpy(x).cuda(), [torch.from_numpy(bias).cuda(), None],
+                                    [g.Activation.NONE, g.Activation.RELU])
+        bufs2.barrier()
+        torch.cuda.synchronize()
+        for y, ww, b, act in ((ya, w, bias, 0), (yb, w2, None, o.ACT_RELU)):
+            ref = o.dense(o.Q4_K, ww, x, b, act, route="f64")
+            err = np.abs(y.cpu().numpy() - ref).max() / np.abs(ref).max()
+            assert err <= 3e-3, (rank, "batch", err)
+        bufs2.barrier()
         q.put((rank, "ok"))
     except Exception as e:
         q.put((rank, repr(e)))
