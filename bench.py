@@ -254,12 +254,13 @@ def run_cuda(args) -> None:
                     g.backend_fused_quantized_dense(x_dev[k], weights[li][pi], None, quant[t], acts[act], out=y_loc[li][pi])
                     dist.all_gather_into_tensor(y_full[li][pi], y_loc[li][pi])
                 elif args.fuse_shared_input and name in ("q", "gate"):
-                    # q+k and gate+up read the same activations and share format and K: one launch each
-                    pj = pi + (1 if name == "q" else 1)
+                    # q, k, v and gate, up read the same activations: one call each.  Matrices of one format
+                    # share a launch (q+k, gate+up); v (Q6_K) runs next to q+k on its share of the SMs.
+                    group = [pi, pi + 1] + ([pi + 2] if (name == "q" and args.fuse_shared_input >= 2) else [])
                     g.backend_fused_quantized_dense_batch(
-                        x_dev[k], [weights[li][pi], weights[li][pj]], None, quant[t],
-                        [acts[act], acts[PROJECTIONS[pj][4]]], outs=[y_loc[li][pi], y_loc[li][pj]])
-                elif args.fuse_shared_input and name in ("k", "up"):
+                        x_dev[k], [weights[li][pj] for pj in group], None, [quant[PROJECTIONS[pj][1]] for pj in group],
+                        [acts[PROJECTIONS[pj][4]] for pj in group], outs=[y_loc[li][pj] for pj in group])
+                elif args.fuse_shared_input and (name in ("k", "up") or (name == "v" and args.fuse_shared_input >= 2)):
                     pass  # computed together with q / gate
                 else:
                     g.backend_fused_quantized_dense(x_dev[k], weights[li][pi], None, quant[t], acts[act], out=y_loc[li][pi])
@@ -369,7 +370,8 @@ def run_cuda(args) -> None:
                                                                    ("4 device barriers per layer" if args.order == "barrier" else "ranks ordered inside the kernels at 4 points per layer")}[gather],
                    "inputs": "fixed N(0,1) activations per projection (outputs not chained)",
                    "l2": f"no flush: {local_bytes / 1e6:.0f} MB of weights per GPU per step exceed the 126 MB L2",
-                   "launch": ("one CUDA graph per step; q+k and gate+up of a layer share one launch each (160 launches)"
+                   "launch": (("one CUDA graph per step; q+k and gate+up of a layer share one launch each (160 launches)" +
+                               ("; v runs next to q+k on its share of the SMs" if (args.fuse_shared_input >= 2 and gather == "none") else ""))
                               if (args.fuse_shared_input and gather in ("none", "peer")) else "one CUDA graph of 224 GEMV launches per step")},
         "roofline": roofline,
         "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": ms_e2e,
@@ -408,8 +410,9 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--fuse-shared-input", type=int, default=1,
-                    help="1: q+k and gate+up (same activations, format and K) run as one launch each")
+    ap.add_argument("--fuse-shared-input", type=int, default=2,
+                    help="1: q+k and gate+up (same activations, format and K) run as one launch each; "
+                         "2: also v (Q6_K) in the q+k call, side by side on its share of the SMs")
     ap.add_argument("--order", default="barrier", choices=["barrier", "kernel"],
                     help="N > 1 with --gather peer: order the ranks with device barriers between launches (default) "
                          "or with completion counters inside the GEMV kernels (experimental)")

@@ -54,6 +54,114 @@ int check_gather_status(const Weight &w, cudaStream_t s) {
 
 using namespace b200q;
 
+extern "C" int b200q_dense(b200q_weight_t h, const void *x_dev, int x_dtype, int64_t m, const float *bias_dev, int activation,
+                           float *y_dev, int64_t y_ld, void *stream);
+
+namespace {
+
+// Side streams and events for launches that run next to each other.  Per host thread and device, so
+// that concurrent callers never share an event.
+struct SideStreams {
+    cudaStream_t stream[3] = {};
+    cudaEvent_t fork = nullptr, join[3] = {};
+    bool ready = false;
+};
+int side_streams(int device, SideStreams **out) {
+    static thread_local SideStreams per_device[16];
+    if (device < 0 || device >= 16) return fail(B200Q_EINVAL, "dense_batch: device index out of range");
+    SideStreams &ss = per_device[device];
+    if (!ss.ready) {
+        B200Q_CUDA(cudaEventCreateWithFlags(&ss.fork, cudaEventDisableTiming));
+        for (int i = 0; i < 3; i++) {
+            B200Q_CUDA(cudaStreamCreateWithFlags(&ss.stream[i], cudaStreamNonBlocking));
+            B200Q_CUDA(cudaEventCreateWithFlags(&ss.join[i], cudaEventDisableTiming));
+        }
+        ss.ready = true;
+    }
+    *out = &ss;
+    return 0;
+}
+
+// b200q_dense_batch for matrices that cannot share one launch.  Decode shapes on one device are grouped by
+// (format, K); every group is one launch, the groups run side by side on forked streams with the SMs divided
+// in proportion to their bytes (small decode launches are bound by latency, not by SM count), and the caller's
+// stream waits for all of them.  Everything else falls back to one b200q_dense call per matrix.
+int dense_batch_mixed(int count, const b200q_weight_t *hs, const std::vector<std::shared_ptr<Weight>> &ws, const void *x_dev,
+                      int x_dtype, int64_t m, const float *const *biases_dev, const int *activations, float *const *ys_dev,
+                      const int64_t *y_lds, void *stream) {
+    bool one_device = true;
+    for (int i = 1; i < count; i++) one_device = one_device && ws[i]->device == ws[0]->device;
+    std::vector<std::vector<int>> groups;
+    if (m <= 16 && one_device) {
+        for (int i = 0; i < count; i++) {
+            bool placed = false;
+            for (auto &g : groups) {
+                if (g.size() < 4 && ws[g[0]]->type == ws[i]->type && ws[g[0]]->k == ws[i]->k) {
+                    g.push_back(i), placed = true;
+                    break;
+                }
+            }
+            if (!placed) groups.push_back({i});
+        }
+    }
+    if (groups.empty() || groups.size() > 4) {
+        for (int i = 0; i < count; i++) {
+            int rc = b200q_dense(hs[i], x_dev, x_dtype, m, biases_dev ? biases_dev[i] : nullptr, activations[i], ys_dev[i],
+                                 y_lds ? y_lds[i] : 0, stream);
+            if (rc != 0) return rc;
+        }
+        return B200Q_OK;
+    }
+    const int device = ws[0]->device;
+    B200Q_CUDA(cudaSetDevice(device));
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    double total = 0;
+    std::vector<double> bytes(groups.size(), 0.0);
+    for (size_t g = 0; g < groups.size(); g++) {
+        for (int i : groups[g]) bytes[g] += (double)ws[i]->bytes;
+        total += bytes[g];
+    }
+    SideStreams *ss = nullptr;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (groups.size() > 1) {
+        int rc = side_streams(device, &ss);
+        if (rc != 0) return rc;
+        B200Q_CUDA(cudaEventRecord(ss->fork, s));
+    }
+    int left = sms;
+    for (size_t g = 0; g < groups.size(); g++) {
+        int share = groups.size() == 1 ? 0 : (int)(sms * bytes[g] / total + 0.5);
+        if (groups.size() > 1) {
+            const int others = (int)(groups.size() - g - 1);
+            share = std::max(8, std::min(share, left - 8 * others));
+            if (others == 0) share = left;
+            left -= share;
+        }
+        cudaStream_t gs = g == 0 ? s : ss->stream[g - 1];
+        if (g > 0) B200Q_CUDA(cudaStreamWaitEvent(gs, ss->fork, 0));
+        const Weight *wp[4];
+        const float *bp[4];
+        float *yp[4];
+        int64_t lds[4];
+        int acts[4];
+        int n = 0;
+        for (int i : groups[g]) {
+            wp[n] = ws[i].get(), bp[n] = biases_dev ? biases_dev[i] : nullptr, yp[n] = ys_dev[i], acts[n] = activations[i];
+            lds[n] = (y_lds && y_lds[i]) ? y_lds[i] : ws[i]->n;
+            n++;
+        }
+        int rc = launch_gemv_batch(n, wp, x_dev, x_dtype, (int)m, bp, acts, yp, lds, gs, nullptr, 0, nullptr, nullptr, 0, 0, share);
+        if (rc != 0) return rc;
+        if (g > 0) B200Q_CUDA(cudaEventRecord(ss->join[g - 1], gs));
+    }
+    for (size_t g = 1; g < groups.size(); g++) B200Q_CUDA(cudaStreamWaitEvent(s, ss->join[g - 1], 0));
+    g_last_kernel = B200Q_KERNEL_GEMV_MMA;
+    return B200Q_OK;
+}
+
+}  // namespace
+
 extern "C" {
 
 int b200q_version(void) { return 100; }
@@ -244,13 +352,10 @@ int b200q_dense_batch(int count, const b200q_weight_t *hs, const void *x_dev, in
         if (y_lds && y_lds[i] != 0 && y_lds[i] < ws[i]->n) return fail(B200Q_EINVAL, "dense_batch: y_ld smaller than N");
         same = same && ws[i]->type == ws[0]->type && ws[i]->k == ws[0]->k && ws[i]->device == ws[0]->device;
     }
-    if (!same) {  // different formats / K, or not a decode shape: one launch per matrix, same results
-        for (int i = 0; i < count; i++) {
-            int rc = b200q_dense(hs[i], x_dev, x_dtype, m, biases_dev ? biases_dev[i] : nullptr, activations[i], ys_dev[i],
-                                 y_lds ? y_lds[i] : 0, stream);
-            if (rc != 0) return rc;
-        }
-        return B200Q_OK;
+    if (!same) {
+        // Different formats / K (q+k in Q4_K next to v in Q6_K), more than four matrices, or not a decode shape.
+        int rc = dense_batch_mixed(count, hs, ws, x_dev, x_dtype, m, biases_dev, activations, ys_dev, y_lds, stream);
+        return rc;
     }
     B200Q_CUDA(cudaSetDevice(ws[0]->device));
     const Weight *wp[4];

@@ -42,12 +42,13 @@ int launch_gather(const Weight &w, const int32_t *idx, int64_t n_idx, float *out
 int launch_gemv(const Weight &w, const void *x, int x_dtype, int m, const float *bias, int act, float *y, int64_t y_ld,
                 cudaStream_t s);
 
-// Up to 4 matrices of one format and K on the same activations in one launch.  y_peer_deltas[r]: byte distance
+// Up to 4 matrices of one format and K on the same activations in one launch.  sm_limit > 0 plans the grid for
+// that many SMs, so that independent launches on other streams find room on the rest of the GPU.  y_peer_deltas[r]: byte distance
 // from every local output element to its copy on peer r (row-sharded layers, all outputs in one symmetric buffer).
 int launch_gemv_batch(int count, const Weight *const *ws, const void *x, int x_dtype, int m, const float *const *biases,
                       const int *acts, float *const *ys, const int64_t *y_lds, cudaStream_t s,
                       const int64_t *y_peer_deltas = nullptr, int npeers = 0, int *sync_local = nullptr,
-                      int *const *sync_peers = nullptr, int rank = 0, int sync_flags = 0);
+                      int *const *sync_peers = nullptr, int rank = 0, int sync_flags = 0, int sm_limit = 0);
 
 // gemm_tcgen05.cu
 int launch_gemm(const Weight &w, const void *x, int x_dtype, int64_t m, const float *bias, int act, float *y,

@@ -98,6 +98,7 @@ struct GemvParams {
     int pre_issue;  // slots requested before the activations are staged (the rest right after)
     int tps;        // tiles per ring slot (one TMA copy)
     int maxunits;   // upper bound on units per CTA (sizes the partial-sum area)
+    int sm_limit;   // host side only: plan for at most this many SMs (0 = all), so that launches can share the GPU
 };
 
 constexpr int kSpinLimit = 1 << 22;
@@ -928,6 +929,7 @@ int launch_t(const Weight &w, const GemvParams &p0, cudaStream_t s) {
     GemvParams p = p0;
     int dev_sms = 148;
     cudaDeviceGetAttribute(&dev_sms, cudaDevAttrMultiProcessorCount, w.device);
+    if (p.sm_limit > 0) dev_sms = std::max(1, std::min(dev_sms, p.sm_limit));
 
     // Two CTAs of up to 8 warps per SM (half the shared memory each) when the staged activations are
     // small: finer load balance, and a dependent launch can move into an SM as soon as one CTA leaves.
@@ -1011,7 +1013,7 @@ int launch_nb(const Weight &w, const GemvParams &p, cudaStream_t s) {
 
 int launch_gemv_batch(int count, const Weight *const *ws, const void *x, int x_dtype, int m, const float *const *biases,
                       const int *acts, float *const *ys, const int64_t *y_lds, cudaStream_t s, const int64_t *y_peer_deltas,
-                      int npeers, int *sync_local, int *const *sync_peers, int rank, int sync_flags) {
+                      int npeers, int *sync_local, int *const *sync_peers, int rank, int sync_flags, int sm_limit) {
     if (m < 1 || m > 16) return fail(B200Q_EINVAL, "gemv: m must be in 1..16");
     if (count < 1 || count > kMaxSegments) return fail(B200Q_EINVAL, "gemv: 1..4 matrices per launch");
     if (npeers < 0 || npeers > 7 || (npeers > 0 && y_peer_deltas == nullptr)) return fail(B200Q_EINVAL, "gemv: bad peer list");
@@ -1027,6 +1029,7 @@ int launch_gemv_batch(int count, const Weight *const *ws, const void *x, int x_d
         rt += w.rt;
     }
     p.nseg = count;
+    p.sm_limit = sm_limit;
     all.rt = rt;
     p.x = x;
     for (int i = 0; i < npeers; i++) p.y_peer_delta[i] = y_peer_deltas[i];

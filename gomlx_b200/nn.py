@@ -216,14 +216,18 @@ def backend_fused_quantized_dense(x, weights, bias, wq: Quantization,
 
 
 def backend_fused_quantized_dense_batch(x, weights, biases, wq: Quantization, activations, outs=None):
-    """Several BackendFusedQuantizedDense nodes on the same activations (q/k/v, gate/up) as one launch
-    (``b200q_dense_batch``).  ``weights``: ResidentWeight list; ``biases``: list with None entries or None;
-    ``activations``: one ActivationType per weight.  Returns the list of ``[m, N_i]`` float32 outputs."""
-    _check_ggml(wq, "BackendFusedQuantizedDense")
+    """Several BackendFusedQuantizedDense nodes on the same activations (q/k/v, gate/up) in one call
+    (``b200q_dense_batch``): matrices of one format and K share a launch, groups of different formats run
+    side by side.  ``weights``: ResidentWeight list; ``wq``: one Quantization or one per weight; ``biases``:
+    list with None entries or None; ``activations``: one ActivationType per weight.  Returns the list of
+    ``[m, N_i]`` float32 outputs."""
+    wqs = list(wq) if isinstance(wq, (list, tuple)) else [wq] * len(weights)
+    for q_ in wqs:
+        _check_ggml(q_, "BackendFusedQuantizedDense")
     if not (torch is not None and isinstance(x, torch.Tensor) and x.is_cuda):
         raise ValueError("the batched form takes CUDA activations")
     dev = x.device.index
-    ws = [resident(w, wq, dev) for w in weights]
+    ws = [resident(w, q_, dev) for w, q_ in zip(weights, wqs)]
     k = ws[0].k
     x2 = x.reshape(-1, k).contiguous()
     m = x2.shape[0]

@@ -124,10 +124,14 @@ int b200q_dense(b200q_weight_t w, const void *x_dev, int x_dtype, int64_t m, con
                 float *y_dev, int64_t y_ld, void *stream);
 
 /* Several FusedQuantizedDense nodes that read the same activations (q/k/v, gate/up of a decoder layer:
- * ml/zoo/transformer/transformer.go:909-924,1286-1294 issue them one after another on the same x), run
- * as one launch when they share format, K and device and m <= 16; otherwise one launch each.  Results are
- * identical to `count` calls of b200q_dense.  biases_dev may be NULL or hold NULL entries; y_lds may be
- * NULL (dense outputs). */
+ * ml/zoo/transformer/transformer.go:909-924,1286-1294 issue them one after another on the same x).  For
+ * m <= 16 on one device, up to four matrices that share format and K run as one launch; groups of different
+ * formats (q and k in Q4_K next to v in Q6_K) run side by side on streams forked from `stream` inside the
+ * call, each planned for its share of the SMs, and `stream` waits for all of them before the call returns
+ * control of it (works under stream capture).  Otherwise one launch per matrix.  Results equal `count` calls
+ * of b200q_dense up to the order in which the partial sums over K are added (the split of K depends on the
+ * launch's row count and SM share): differences stay at f32 rounding level and every call is deterministic.
+ * biases_dev may be NULL or hold NULL entries; y_lds may be NULL (dense outputs). */
 int b200q_dense_batch(int count, const b200q_weight_t *ws, const void *x_dev, int x_dtype, int64_t m,
                       const float *const *biases_dev, const int *activations, float *const *ys_dev, const int64_t *y_lds,
                       void *stream);

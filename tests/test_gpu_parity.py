@@ -250,7 +250,7 @@ def test_batched_projections_match_single_launches(oracle, name, m):
         want = g.backend_fused_quantized_dense(x, w, b, quant(t), a)
         assert y.shape == want.shape
         assert float((y - want).abs().max()) <= 1e-5 * max(1.0, float(want.abs().max()))
-    # mixed formats fall back to one launch per matrix with the same results
+    # mixed formats: one launch per format group, side by side on forked streams (legacy default stream here)
     other = g.upload(oracle.make_weights(14, 48, k, seed=3), g.GGMLQuantType.Q6_K)
     y2 = torch.empty(m, 48, device="cuda")
     hs = (ctypes.c_uint64 * 2)(ws[0].handle, other.handle)
@@ -259,8 +259,46 @@ def test_batched_projections_match_single_launches(oracle, name, m):
     assert nat.lib().b200q_dense_batch(2, hs, ctypes.c_void_p(x.data_ptr()), nat.F32, m, None, aa, ya, None, None) == 0
     torch.cuda.synchronize()
     want = g.backend_fused_quantized_dense(x, other, None, quant(g.GGMLQuantType.Q6_K))
-    assert torch.equal(y2, want)
+    assert float((y2 - want).abs().max()) <= 1e-5 * max(1.0, float(want.abs().max()))
     for w in ws + [other]:
+        w.free()
+
+
+@pytest.mark.parametrize("m", [1, 8])
+def test_mixed_format_batch_side_by_side(oracle, m):
+    """q+k (Q4_K) and v (Q6_K) of a decoder layer in one call: two launches on forked streams, also when the
+    call is captured into a CUDA graph; the caller's stream sees all results."""
+    k = 2048
+    specs = [("Q4_K", 1024), ("Q4_K", 256), ("Q6_K", 256)]
+    raw = [oracle.make_weights(int(TYPES[name]), n, k, seed=40 + i) for i, (name, n) in enumerate(specs)]
+    ws = [g.upload(w, TYPES[name]) for w, (name, _) in zip(raw, specs)]
+    qs = [quant(TYPES[name]) for name, _ in specs]
+    rng = np.random.default_rng(5 + m)
+    xn = rng.standard_normal((m, k)).astype(np.float32)
+    x = torch.from_numpy(xn).cuda()
+    acts = [g.ActivationType.NONE] * 3
+    outs = g.backend_fused_quantized_dense_batch(x, ws, None, qs, acts)
+    torch.cuda.synchronize()
+    for y, w, (name, _) in zip(outs, raw, specs):
+        ref = oracle.dense(int(TYPES[name]), w, xn, route="f64")
+        assert rel_err(y.cpu().numpy(), ref) <= TOL_GEMV
+    # the same call inside a graph: replays must reproduce the eager results on fresh inputs
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        g.backend_fused_quantized_dense_batch(x, ws, None, qs, acts, outs=outs)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        g.backend_fused_quantized_dense_batch(x, ws, None, qs, acts, outs=outs)
+    eager = [y.clone() for y in outs]
+    x.mul_(2.0)
+    graph.replay()
+    torch.cuda.synchronize()
+    for y, e in zip(outs, eager):
+        assert float((y - 2.0 * e).abs().max()) <= 2e-3 * float(e.abs().max())
+    for w in ws:
         w.free()
 
 
