@@ -34,7 +34,8 @@ def _worker(rank, world, port, q):
         w = o.make_weights(o.Q4_K, n, k, seed=1)
         rng = np.random.default_rng(2)
         bias = rng.standard_normal(n).astype(np.float32)
-        bufs = PeerScatterBuffers(max_m * n, rank)
+        n2 = 512 + 16
+        bufs = PeerScatterBuffers(max_m * (n + n2), rank)  # one symmetric allocation for both parts of the test
         layer = PeerScatterDense(w, quant, bufs, 0, max_m, rank)
         for m in (1, 5):
             x = rng.standard_normal((m, k)).astype(np.float32)
@@ -47,21 +48,19 @@ def _worker(rank, world, port, q):
             assert err <= 3e-3, (rank, m, err)
             bufs.barrier()  # nobody overwrites the buffers while a peer still reads them
         # two projections on the same activations in one launch (q+k / gate+up), regions of one buffer
-        n2 = 512 + 16
         w2 = o.make_weights(o.Q4_K, n2, k, seed=3)
-        bufs2 = PeerScatterBuffers(max_m * (n + n2), rank)
-        la = PeerScatterDense(w, quant, bufs2, 0, max_m, rank)
-        lb = PeerScatterDense(w2, quant, bufs2, max_m * n, max_m, rank)
+        la = layer
+        lb = PeerScatterDense(w2, quant, bufs, max_m * n, max_m, rank)
         x = rng.standard_normal((3, k)).astype(np.float32)
         ya, yb = peer_scatter_batch([la, lb], torch.from_numpy(x).cuda(), [torch.from_numpy(bias).cuda(), None],
                                     [g.Activation.NONE, g.Activation.RELU])
-        bufs2.barrier()
+        bufs.barrier()
         torch.cuda.synchronize()
         for y, ww, b, act in ((ya, w, bias, 0), (yb, w2, None, o.ACT_RELU)):
             ref = o.dense(o.Q4_K, ww, x, b, act, route="f64")
             err = np.abs(y.cpu().numpy() - ref).max() / np.abs(ref).max()
             assert err <= 3e-3, (rank, "batch", err)
-        bufs2.barrier()
+        bufs.barrier()
         q.put((rank, "ok"))
     except Exception as e:
         q.put((rank, repr(e)))
@@ -80,7 +79,7 @@ def test_two_gpu_peer_scatter(oracle):
     procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    results = [q.get(timeout=240) for _ in procs]
+    results = [q.get(timeout=120) for _ in procs]
     for p in procs:
         p.join(30)
     assert sorted(results) == [(0, "ok"), (1, "ok")], results
