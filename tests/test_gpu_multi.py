@@ -37,6 +37,7 @@ def _worker(rank, world, port, q):
         n2 = 512 + 16
         bufs = PeerScatterBuffers(max_m * (n + n2), rank)  # one symmetric allocation for both parts of the test
         layer = PeerScatterDense(w, quant, bufs, 0, max_m, rank)
+        bad = []  # numeric failures are reported after the last barrier, so that no rank waits for one that left
         for m in (1, 5):
             x = rng.standard_normal((m, k)).astype(np.float32)
             y = layer(torch.from_numpy(x).cuda(), torch.from_numpy(bias).cuda(), g.Activation.SILU)
@@ -45,23 +46,25 @@ def _worker(rank, world, port, q):
             ref = o.dense(o.Q4_K, w, x, bias, o.ACT_SILU, route="f64")
             pre = o.dense(o.Q4_K, w, x, bias, 0, route="f64")
             err = np.abs(y.cpu().numpy() - ref).max() / np.abs(pre).max()
-            assert err <= 3e-3, (rank, m, err)
+            if not err <= 3e-3:
+                bad.append((rank, m, float(err)))
             bufs.barrier()  # nobody overwrites the buffers while a peer still reads them
         # two projections on the same activations in one launch (q+k / gate+up), regions of one buffer
         w2 = o.make_weights(o.Q4_K, n2, k, seed=3)
-        la = layer
         lb = PeerScatterDense(w2, quant, bufs, max_m * n, max_m, rank)
         x = rng.standard_normal((3, k)).astype(np.float32)
-        ya, yb = peer_scatter_batch([la, lb], torch.from_numpy(x).cuda(), [torch.from_numpy(bias).cuda(), None],
+        ya, yb = peer_scatter_batch([layer, lb], torch.from_numpy(x).cuda(), [torch.from_numpy(bias).cuda(), None],
                                     [g.Activation.NONE, g.Activation.RELU])
         bufs.barrier()
         torch.cuda.synchronize()
         for y, ww, b, act in ((ya, w, bias, 0), (yb, w2, None, o.ACT_RELU)):
             ref = o.dense(o.Q4_K, ww, x, b, act, route="f64")
             err = np.abs(y.cpu().numpy() - ref).max() / np.abs(ref).max()
-            assert err <= 3e-3, (rank, "batch", err)
+            if not err <= 3e-3:
+                bad.append((rank, "batch", float(err)))
         bufs.barrier()
-        q.put((rank, "ok"))
+        torch.cuda.synchronize()
+        q.put((rank, "ok" if not bad else repr(bad)))
     except Exception as e:
         q.put((rank, repr(e)))
     finally:
