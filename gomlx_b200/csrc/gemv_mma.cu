@@ -602,6 +602,207 @@ __device__ __forceinline__ void stage_x(const GemvParams &p, int64_t k0, int kc,
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Integer path (m = 1, Q4_K): the weights' 4-bit codes go into the tensor cores as they are.
+//
+// Activations are quantized per 32-value sub-block to 15-bit fixed point, xq = round(x / s) with
+// |xq| <= 16319, and split into two signed 8-bit digits, xq = 128 * hi + lo (lo in -64..63).  One
+// m16n8k32 integer MMA multiplies 8 codes per lane and row with both digits at once: its 8 output
+// columns are used as (K quarter t of the lane quad) x (digit), i.e. the B operand of lane (g, t) is
+// the hi digits of quarter t's activations when g == 2t, the lo digits when g == 2t + 1 and zero
+// otherwise.  Every lane then holds, exactly, the integer dot products of ITS OWN two rows and
+// sub-block, so the block scale is applied after the MMA in f32:
+//     y_row += (d * sc) * s * (128 * S_hi + S_lo)  -  (dmin * m) * s * sum(xq)
+// No magic offsets, no per-value scaling and no fp16 rounding of weights remain; unpacking costs one
+// AND per four low nibbles and a shift + AND per four high nibbles.  The activation error is
+// |x - s * xq| <= max|x_block| / 32638.
+//
+// Staged activations of a K slice: three byte arrays (hi digits, lo digits, zeros), one byte per
+// value, each tile padded from 256 to 272 bytes and its quarters 2, 3 shifted by 16 so that the eight
+// lanes that read real digits hit eight different 16-byte bank groups; then s and s * sum(xq) per
+// sub-block as f32.
+// ---------------------------------------------------------------------------------------
+constexpr int kXqMax = 16319;   // 127 * 128 + 63
+
+// Per format: BLK = values that share an activation scale (the format's sub-block), PAD = bytes by which the
+// second half of a tile is shifted (tile pitch 256 + PAD), LO = offset of the lo array modulo 128.  Chosen so
+// that the eight lanes reading real digits in one instruction hit eight different 16-byte bank groups:
+//   Q4_K  lane quarter t reads at 64t (+16 for t >= 2): {0, 64, 16, 80}, lo array +32
+//   Q6_K  lane t = 2n + lh reads at 128n + 16lh (+32 for n = 1): {0, 16, 32, 48}, lo array +64
+template <int TYPE> struct I8Fmt;
+template <> struct I8Fmt<kQ4_K> { static constexpr int BLK = 32, PAD = 16, LO = 32; };
+template <> struct I8Fmt<kQ6_K> { static constexpr int BLK = 16, PAD = 32, LO = 64; };
+template <int TYPE> struct I8Fmt { static constexpr int BLK = 32, PAD = 16, LO = 32; };  // unused for other formats
+
+template <int TYPE>
+__device__ __forceinline__ int dig_pos(int k) {  // byte position of slice value k inside a digit array
+    return (k >> 8) * (256 + I8Fmt<TYPE>::PAD) + (k & 255) + ((k >> 7) & 1) * I8Fmt<TYPE>::PAD;
+}
+template <int TYPE>
+__host__ __device__ inline size_t dig_array_bytes(int kts) { return ((size_t)kts * (256 + I8Fmt<TYPE>::PAD) + 127) & ~(size_t)127; }
+// Offsets of the three arrays: hi at 0, lo at L + LO, zeros at 2L + 2*LO.
+template <int TYPE>
+__host__ __device__ inline size_t dig_region_bytes(int kts) { return 3 * dig_array_bytes<TYPE>(kts) + 128; }
+
+__device__ __forceinline__ void imma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Quantizes x[k0 .. k0+kc) of one batch row into the digit arrays (see above).  A thread handles 8
+// values, BLK / 8 neighbouring threads one sub-block.
+template <int TYPE>
+__device__ __forceinline__ void stage_x_i8(const GemvParams &p, int64_t k0, int kc, uint8_t *dig, float *sx, float *xsum) {
+    constexpr int BLK = I8Fmt<TYPE>::BLK, TPB = BLK / 8;  // threads per sub-block
+    const size_t L = dig_array_bytes<TYPE>(kc >> 8);
+    uint8_t *hi = dig, *lo = dig + L + I8Fmt<TYPE>::LO, *zero = dig + 2 * L + 2 * I8Fmt<TYPE>::LO;
+    const int gpc = kc >> 3;
+    for (int gi = threadIdx.x; gi < gpc; gi += blockDim.x) {
+        const int64_t k = k0 + (int64_t)gi * 8;
+        float v[8];
+        if (k < p.k) {
+            if (p.x_dtype == B200Q_F32) {
+                const float4 *src = reinterpret_cast<const float4 *>(static_cast<const float *>(p.x) + k);
+                const float4 a = __ldg(src), b = __ldg(src + 1);
+                v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+            } else {
+                const uint4 r = __ldg(reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.x) + k));
+                const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) v[2 * i] = __uint_as_float(w[i] << 16), v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = 0.0f;
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));  // fmaxf drops NaNs
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        if constexpr (TPB == 4) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fminf(amax, 65504.0f);  // same saturation as the fp16 path: larger values clamp to the block maximum
+        const float inv = amax > 0.0f ? (float)kXqMax / amax : 0.0f;
+        int h[8], l[8], sum = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            // |v * inv| <= 16319 unless v was beyond the saturation point (or NaN, which converts to 0)
+            const int xq = max(-kXqMax, min(kXqMax, __float2int_rn(v[i] * inv)));
+            h[i] = (xq + 64) >> 7, l[i] = xq - (h[i] << 7);
+            sum += xq;
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        if constexpr (TPB == 4) sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        auto pack4 = [](int a, int b, int c, int d) {  // low bytes of four ints
+            return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+        };
+        const int pos = dig_pos<TYPE>(gi * 8);
+        *reinterpret_cast<uint2 *>(hi + pos) = make_uint2(pack4(h[0], h[1], h[2], h[3]), pack4(h[4], h[5], h[6], h[7]));
+        *reinterpret_cast<uint2 *>(lo + pos) = make_uint2(pack4(l[0], l[1], l[2], l[3]), pack4(l[4], l[5], l[6], l[7]));
+        *reinterpret_cast<uint2 *>(zero + pos) = make_uint2(0u, 0u);
+        if ((gi & (TPB - 1)) == 0) {
+            const float sc = amax * (1.0f / (float)kXqMax);
+            sx[gi / TPB] = sc;
+            xsum[gi / TPB] = sc * (float)sum;
+        }
+    }
+}
+
+// d * sc and dmin * m of sub-blocks 2t and 2t+1 of one Q4_K row header, in f32.
+__device__ __forceinline__ void q4k_scales_f32(const uint4 &h, int t, float &ds_lo, float &ds_hi, float &dm_lo, float &dm_hi) {
+    const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xFFFFu)));
+    const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
+    uint32_t sc2, mn2;  // bytes 0 and 1: the 6-bit fields of sub-blocks 2t, 2t+1
+    if (t < 2) {
+        sc2 = (h.y >> (16 * t)) & 0x3F3Fu;
+        mn2 = (h.z >> (16 * t)) & 0x3F3Fu;
+    } else {
+        const int u = 16 * (t - 2);
+        const uint32_t n = h.w >> u;  // low nibbles: scales, high nibbles: mins
+        sc2 = (n & 0x0F0Fu) | (((h.y >> u) >> 2) & 0x3030u);
+        mn2 = ((n >> 4) & 0x0F0Fu) | (((h.z >> u) >> 2) & 0x3030u);
+    }
+    ds_lo = d * (float)(sc2 & 0xFFu), ds_hi = d * (float)(sc2 >> 8);
+    dm_lo = dmin * (float)(mn2 & 0xFFu), dm_hi = dmin * (float)(mn2 >> 8);
+}
+
+// One 16 x 256 Q4_K tile, integer path.  dig: this lane's digit array at the tile's quarter t (or the zero
+// array); sxp / xsp: shared-memory addresses of s and s*sum(xq) of the tile's sub-blocks 2t, 2t+1.
+__device__ __forceinline__ void tile_q4_k_i8(uint32_t tile, int lane, uint32_t dig, uint32_t sxp, uint32_t xsp, float &yg, float &yg8) {
+    const int g = lane >> 2, t = lane & 3;
+    float ds_lo, ds_hi, dm_lo, dm_hi, ds_lo8, ds_hi8, dm_lo8, dm_hi8;
+    q4k_scales_f32(lds128(tile + g * 16), t, ds_lo, ds_hi, dm_lo, dm_hi);
+    q4k_scales_f32(lds128(tile + (g + 8) * 16), t, ds_lo8, ds_hi8, dm_lo8, dm_hi8);
+    int cl[4] = {0, 0, 0, 0}, ch[4] = {0, 0, 0, 0};  // (row g: hi, lo digit), (row g+8: hi, lo digit)
+    constexpr uint32_t M = 0x0F0F0F0Fu;
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const uint4 qa = lds128(tile + 256 + (2 * i) * 512 + lane * 16);
+        const uint4 qb = lds128(tile + 256 + (2 * i + 1) * 512 + lane * 16);
+        const uint4 dl = lds128(dig + 16 * i), dh = lds128(dig + 32 + 16 * i);
+        imma_u8s8(cl, qa.x & M, qb.x & M, qa.y & M, qb.y & M, dl.x, dl.y);
+        imma_u8s8(cl, qa.z & M, qb.z & M, qa.w & M, qb.w & M, dl.z, dl.w);
+        imma_u8s8(ch, (qa.x >> 4) & M, (qb.x >> 4) & M, (qa.y >> 4) & M, (qb.y >> 4) & M, dh.x, dh.y);
+        imma_u8s8(ch, (qa.z >> 4) & M, (qb.z >> 4) & M, (qa.w >> 4) & M, (qb.w >> 4) & M, dh.z, dh.w);
+    }
+    const uint2 s2 = lds64(sxp), x2 = lds64(xsp);
+    const float sl = __uint_as_float(s2.x), sh = __uint_as_float(s2.y), xl = __uint_as_float(x2.x), xh = __uint_as_float(x2.y);
+    yg += (ds_lo * sl) * (float)(128 * cl[0] + cl[1]) - dm_lo * xl + (ds_hi * sh) * (float)(128 * ch[0] + ch[1]) - dm_hi * xh;
+    yg8 += (ds_lo8 * sl) * (float)(128 * cl[2] + cl[3]) - dm_lo8 * xl + (ds_hi8 * sh) * (float)(128 * ch[2] + ch[3]) - dm_hi8 * xh;
+}
+
+// d * scale of the lane's four sub-blocks (8n + lh + 2c, c = 0..3) of one Q6_K row, in f32.
+__device__ __forceinline__ void q6k_scales_f32(const uint2 &s, int lh, float d, float (&ds)[4]) {
+    const uint32_t lo = lh ? s.x >> 8 : s.x, hi = lh ? s.y >> 8 : s.y;  // bytes 0 and 2: scales of c = 0, 1 | 2, 3
+    ds[0] = d * (float)(int)(int8_t)(lo & 0xFFu), ds[1] = d * (float)(int)(int8_t)((lo >> 16) & 0xFFu);
+    ds[2] = d * (float)(int)(int8_t)(hi & 0xFFu), ds[3] = d * (float)(int)(int8_t)((hi >> 16) & 0xFFu);
+}
+
+// One 16 x 256 Q6_K tile, integer path.  Lane t = 2n + lh owns values 128n + 32c + 16lh + 0..15, c = 0..3, of
+// rows g and g+8: four 16-value sub-blocks, each two integer MMAs.  dig: the lane's digit array at the tile's
+// offset 128n + 16lh (+ padding); sxp / xsp: s and s*sum(xq) of sub-block 8n + lh (the others 2c further).
+__device__ __forceinline__ void tile_q6_k_i8(uint32_t tile, int lane, uint32_t dig, uint32_t sxp, uint32_t xsp, float &yg, float &yg8) {
+    const int g = lane >> 2, t = lane & 3, n = t >> 1, lh = t & 1;
+    const float dg = __half2float(__ushort_as_half((unsigned short)lds16(tile + 3328 + g * 2)));
+    const float dg8 = __half2float(__ushort_as_half((unsigned short)lds16(tile + 3328 + (g + 8) * 2)));
+    float ds[4], ds8[4];
+    q6k_scales_f32(lds64(tile + g * 16 + 8 * n), lh, dg, ds);
+    q6k_scales_f32(lds64(tile + (g + 8) * 16 + 8 * n), lh, dg8, ds8);
+    const uint4 la = lds128(tile + 256 + 0 * 512 + lane * 16), la8 = lds128(tile + 256 + 1 * 512 + lane * 16);
+    const uint4 lb = lds128(tile + 256 + 2 * 512 + lane * 16), lb8 = lds128(tile + 256 + 3 * 512 + lane * 16);
+    const uint4 hh = lds128(tile + 256 + 4 * 512 + lane * 16), hh8 = lds128(tile + 256 + 5 * 512 + lane * 16);
+    int acc[4][4] = {};  // [c][(row g: hi, lo digit), (row g+8: hi, lo digit)]
+    constexpr uint32_t ML = 0x0F0F0F0Fu, MH = 0x30303030u;
+    uint4 dgt[4];
+#pragma unroll
+    for (int c = 0; c < 4; c++) dgt[c] = lds128(dig + 32 * c);
+#pragma unroll
+    for (int half = 0; half < 2; half++) {  // words (0, 1) then (2, 3) of every 16-byte piece
+        uint32_t code[2][4], code8[2][4];
+#pragma unroll
+        for (int w2 = 0; w2 < 2; w2++) {
+            const int wp = half, ww = w2;
+            const uint32_t a = B200Q_WORD(la, wp, ww), a8 = B200Q_WORD(la8, wp, ww);
+            const uint32_t bq = B200Q_WORD(lb, wp, ww), bq8 = B200Q_WORD(lb8, wp, ww);
+            const uint32_t h = B200Q_WORD(hh, wp, ww), h8 = B200Q_WORD(hh8, wp, ww);
+            code[w2][0] = (a & ML) | ((h << 4) & MH), code[w2][1] = (bq & ML) | ((h << 2) & MH);
+            code[w2][2] = ((a >> 4) & ML) | (h & MH), code[w2][3] = ((bq >> 4) & ML) | ((h >> 2) & MH);
+            code8[w2][0] = (a8 & ML) | ((h8 << 4) & MH), code8[w2][1] = (bq8 & ML) | ((h8 << 2) & MH);
+            code8[w2][2] = ((a8 >> 4) & ML) | (h8 & MH), code8[w2][3] = ((bq8 >> 4) & ML) | ((h8 >> 2) & MH);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; c++)
+            imma_u8s8(acc[c], code[0][c], code8[0][c], code[1][c], code8[1][c], half == 0 ? dgt[c].x : dgt[c].z,
+                      half == 0 ? dgt[c].y : dgt[c].w);
+    }
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        const float sc = __uint_as_float(lds32(sxp + 8 * c)), xs = __uint_as_float(lds32(xsp + 8 * c));
+        yg += ds[c] * (sc * (float)(128 * acc[c][0] + acc[c][1]) - 32.0f * xs);
+        yg8 += ds8[c] * (sc * (float)(128 * acc[c][2] + acc[c][3]) - 32.0f * xs);
+    }
+}
+
 // Matrix that launch-wide row tile `rt` belongs to.
 __device__ __forceinline__ int segment_of(const GemvParams &p, int rt) {
     int s = 0;
@@ -614,8 +815,10 @@ __device__ __forceinline__ int segment_of(const GemvParams &p, int rt) {
 // Inside a CTA the work is cut into units = (row tile, k part); warp w takes units w, w + nwarps, ...
 // and streams each unit's tiles through its private ring of shared-memory slots.
 // Shared memory: staged x | aux sums | partial sums per unit | tile rings | mbarriers.
-template <int TYPE, int NB>
+template <int TYPE, int NB, bool I8>
 __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
+    static_assert(!I8 || ((TYPE == kQ4_K || TYPE == kQ6_K) && NB == 1), "the integer path exists for Q4_K and Q6_K at m = 1");
+    using IF = I8Fmt<TYPE>;
     using F = Fmt<TYPE>;
     extern __shared__ __align__(128) uint8_t smem[];
     B200Q_TRACE_POINT(0);
@@ -629,10 +832,19 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
     const int ns = F::SUB ? kc / F::SUB : 0;
     size_t off = 0;
     __half *xs = reinterpret_cast<__half *>(smem);
-    off += (size_t)p.m * xs_stride * 2;
-    __half *shi = reinterpret_cast<__half *>(smem + off);
-    __half *slo = shi + (size_t)p.m * ns;
-    off += (size_t)p.m * ns * 4;
+    __half *shi = nullptr, *slo = nullptr;
+    float *sx = nullptr, *xsum = nullptr;  // integer path: s and s * sum(xq) per 32-value sub-block
+    if constexpr (I8) {
+        off += dig_region_bytes<TYPE>(p.kts);
+        sx = reinterpret_cast<float *>(smem + off);
+        xsum = sx + kc / IF::BLK;
+        off += (size_t)(kc / IF::BLK) * 8;
+    } else {
+        off += (size_t)p.m * xs_stride * 2;
+        shi = reinterpret_cast<__half *>(smem + off);
+        slo = shi + (size_t)p.m * ns;
+        off += (size_t)p.m * ns * 4;
+    }
     off = (off + 15) & ~(size_t)15;
     float *red = reinterpret_cast<float *>(smem + off);  // [unit][nb][i][lane]
     off += (size_t)p.maxunits * NB * 128 * sizeof(float);
@@ -709,6 +921,16 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
     } else {
         lane_chunk = 8 * t, swz_a = (t & 1) * 32, swz_b = (t >> 1) * 64;
     }
+    // integer path: this lane's digit array (hi digits if g == 2t, lo digits if g == 2t+1, else zeros)
+    uint32_t dig_lane = 0, sx_lane = 0, xs_lane = 0;
+    if constexpr (I8) {
+        const uint32_t L = (uint32_t)dig_array_bytes<TYPE>(p.kts), base = smem_u32(smem);
+        // offset of the lane's values inside a tile, and of its first sub-block's scale
+        const int voff = TYPE == kQ4_K ? 64 * t + IF::PAD * (t >> 1) : 128 * (t >> 1) + 16 * (t & 1) + IF::PAD * (t >> 1);
+        const int soff = TYPE == kQ4_K ? 8 * t : 4 * (8 * (t >> 1) + (t & 1));
+        dig_lane = g == 2 * t ? base + voff : g == 2 * t + 1 ? base + L + IF::LO + voff : base + 2 * L + 2 * IF::LO;
+        sx_lane = smem_u32(sx) + soff, xs_lane = smem_u32(xsum) + soff;
+    }
     XBase<NB> xb;
 #pragma unroll
     for (int nb = 0; nb < NB; nb++) {
@@ -741,7 +963,13 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
         }
         __syncthreads();
     }
-    if (kt_begin < kt_end) stage_x<TYPE>(p, (int64_t)kt_begin * F::TK, (kt_end - kt_begin) * F::TK, xs_stride, ns, xs, shi, slo);
+    if (kt_begin < kt_end) {
+        if constexpr (I8) {
+            stage_x_i8<TYPE>(p, (int64_t)kt_begin * F::TK, (kt_end - kt_begin) * F::TK, smem, sx, xsum);
+        } else {
+            stage_x<TYPE>(p, (int64_t)kt_begin * F::TK, (kt_end - kt_begin) * F::TK, xs_stride, ns, xs, shi, slo);
+        }
+    }
     __syncthreads();
     if (lane == 0)
         for (; issued0 < p.depth && prow < nrows; issued0++) issue_next();
@@ -764,6 +992,10 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
         // The activation addresses of the unit's first tile; every further tile is a constant step on.
         XCols<NB> xc;
         xcols_for_tile<NB>(xc, xb, (k0 - kt_begin) * 32, F::SUB ? (k0 - kt_begin) * (F::TK / F::SUB) : 0, swz_a, swz_b);
+        float yg = 0.0f, yg8 = 0.0f;  // integer path: rows g and g+8, this lane's K quarter
+        constexpr int kDigTile = 256 + IF::PAD, kScaleTile = 256 / IF::BLK * 4;  // bytes per tile: digits, scales
+        uint32_t dig = dig_lane + (k0 - kt_begin) * kDigTile, sxp = sx_lane + (k0 - kt_begin) * kScaleTile,
+                 xsp = xs_lane + (k0 - kt_begin) * kScaleTile;
         for (int left = k1 - k0; left > 0;) {
             const int nt = min(p.tps, left);
             if (!mbar_wait(bars_s + 8 * cd, cphase)) timed_out = true;
@@ -772,7 +1004,14 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
 #endif
             uint32_t tile = cslot;
             for (int ti = 0; ti < nt; ti++) {
-                if constexpr (TYPE == kQ4_0) {
+                if constexpr (I8) {
+                    if constexpr (TYPE == kQ4_K) {
+                        tile_q4_k_i8(tile, lane, dig, sxp, xsp, yg, yg8);
+                    } else {
+                        tile_q6_k_i8(tile, lane, dig, sxp, xsp, yg, yg8);
+                    }
+                    dig += kDigTile, sxp += kScaleTile, xsp += kScaleTile;
+                } else if constexpr (TYPE == kQ4_0) {
                     tile_q4_0<NB>(tile, lane, xc, nc, acc);
                 } else if constexpr (TYPE == kQ8_0) {
                     tile_q8_0<NB>(tile, lane, xc, acc);
@@ -797,6 +1036,11 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 issue_next();
             }
+        }
+        if constexpr (I8) {  // add the four K quarters of a row; lane t = 0 holds batch column 0 of rows g, g+8
+            yg += __shfl_xor_sync(0xffffffffu, yg, 1), yg8 += __shfl_xor_sync(0xffffffffu, yg8, 1);
+            yg += __shfl_xor_sync(0xffffffffu, yg, 2), yg8 += __shfl_xor_sync(0xffffffffu, yg8, 2);
+            acc[0][0][0] = t == 0 ? yg : 0.0f, acc[0][0][2] = t == 0 ? yg8 : 0.0f;
         }
         float *r = red + (size_t)(crow * p.kp + cpart) * NB * 128 + lane;
 #pragma unroll
@@ -923,7 +1167,7 @@ Plan make_plan(int64_t rt, int64_t kt, int sms, int max_warps, size_t x_bytes_pe
     return best;
 }
 
-template <int TYPE, int NB>
+template <int TYPE, int NB, bool I8>
 int launch_t(const Weight &w, const GemvParams &p0, cudaStream_t s) {
     using F = Fmt<TYPE>;
     GemvParams p = p0;
@@ -933,7 +1177,8 @@ int launch_t(const Weight &w, const GemvParams &p0, cudaStream_t s) {
 
     // Two CTAs of up to 8 warps per SM (half the shared memory each) when the staged activations are
     // small: finer load balance, and a dependent launch can move into an SM as soon as one CTA leaves.
-    const size_t x_per_ktile = (size_t)p.m * (F::TK * 2 + (F::SUB ? 4 * (F::TK / F::SUB) : 0));
+    const size_t x_per_ktile = I8 ? (size_t)(3 * (256 + I8Fmt<TYPE>::PAD) + 2 * 4 * (256 / I8Fmt<TYPE>::BLK) + 16)
+                                  : (size_t)p.m * (F::TK * 2 + (F::SUB ? 4 * (F::TK / F::SUB) : 0));
     const size_t x_whole = x_per_ktile * (size_t)w.kt;
     int cps = 1;
     (void)x_whole;
@@ -962,7 +1207,8 @@ int launch_t(const Weight &w, const GemvParams &p0, cudaStream_t s) {
     p.tps = std::max(1, std::min(p.ktp, env_int("B200Q_GEMV_TPS", F::TILE <= 2304 ? 2 : 1)));
 
     const size_t x_bytes =
-        (((size_t)p.m * (p.kts * F::TK + 8) * 2 + (F::SUB ? (size_t)p.m * (p.kts * F::TK / F::SUB) * 4 : 0)) + 15) & ~(size_t)15;
+        I8 ? ((dig_region_bytes<TYPE>(p.kts) + (size_t)p.kts * 2 * 4 * (256 / I8Fmt<TYPE>::BLK) + 15) & ~(size_t)15)
+           : ((((size_t)p.m * (p.kts * F::TK + 8) * 2 + (F::SUB ? (size_t)p.m * (p.kts * F::TK / F::SUB) * 4 : 0)) + 15) & ~(size_t)15);
     const size_t red_bytes = (size_t)p.maxunits * NB * 128 * sizeof(float);
     const size_t fixed = (x_bytes + red_bytes + 127) & ~(size_t)127;
     const size_t slot_bytes = (size_t)p.tps * F::TILE;
@@ -980,7 +1226,7 @@ int launch_t(const Weight &w, const GemvParams &p0, cudaStream_t s) {
     p.pre_issue = std::max(1, std::min(depth, env_int("B200Q_GEMV_PRE", depth)));
     const size_t smem = fixed + (size_t)warps * depth * slot_bytes + (size_t)warps * depth * 8;
 
-    auto kern = gemv_mma_kernel<TYPE, NB>;
+    auto kern = gemv_mma_kernel<TYPE, NB, I8>;
     static thread_local bool configured[16] = {};
     if (!configured[w.device & 15]) {
         B200Q_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit));
@@ -1006,7 +1252,16 @@ int launch_t(const Weight &w, const GemvParams &p0, cudaStream_t s) {
 
 template <int TYPE>
 int launch_nb(const Weight &w, const GemvParams &p, cudaStream_t s) {
-    return p.m <= 8 ? launch_t<TYPE, 1>(w, p, s) : launch_t<TYPE, 2>(w, p, s);
+    if constexpr (TYPE == kQ4_K || TYPE == kQ6_K) {
+        // m = 1: integer tensor-core path (B200Q_GEMV_I8=0 selects the fp16 path, for comparisons)
+        // Quantizing the activations costs every CTA more than staging them as fp16 (measured: about 1.5 us
+        // per launch against 0.034 us saved per tile and SM), so the path pays from about 44 tiles per SM.
+        // (read at every launch so that tests can force either path: 0 = never, 1 = by size, 2 = always)
+        const int i8 = env_int("B200Q_GEMV_I8", 1);
+        const int i8_min_tiles = env_int("B200Q_GEMV_I8_MIN_TILES", 44);
+        if (i8 != 0 && p.m == 1 && (i8 == 2 || w.rt * w.kt >= (int64_t)i8_min_tiles * 148)) return launch_t<TYPE, 1, true>(w, p, s);
+    }
+    return p.m <= 8 ? launch_t<TYPE, 1, false>(w, p, s) : launch_t<TYPE, 2, false>(w, p, s);
 }
 
 }  // namespace

@@ -302,6 +302,69 @@ def test_mixed_format_batch_side_by_side(oracle, m):
         w.free()
 
 
+# ----------------------------------------------------------------------------- integer decode path
+@pytest.fixture
+def force_integer_path(monkeypatch):
+    """The m = 1 integer tensor-core path is chosen by matrix size; tests force it on small matrices."""
+    monkeypatch.setenv("B200Q_GEMV_I8", "2")
+
+
+@pytest.mark.parametrize("name", ["Q4_K", "Q6_K"])
+@pytest.mark.parametrize("n,k", [(16, 256), (100, 512), (1000, 2048), (272, 4096), (64, 14336)])
+def test_integer_path_parity(oracle, force_integer_path, name, n, k):
+    t = TYPES[name]
+    w = oracle.make_weights(int(t), n, k, seed=n + k)
+    rng = np.random.default_rng(n * 7 + k)
+    x = rng.standard_normal((1, k)).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    ref = oracle.dense(int(t), w, x, bias, 0, route="f64")
+    wr = g.upload(w, t)
+    y = g.quantized_dense(torch.from_numpy(x).cuda(), wr, quant(t), torch.from_numpy(bias).cuda())
+    assert g.last_kernel() == nat.KERNEL_GEMV_MMA
+    assert nat.lib().b200q_weight_check(wr.handle, None) == 0
+    assert rel_err(y.cpu().numpy(), ref) <= 2e-4   # 15-bit activations, exact codes and f32 scales
+    yb = g.quantized_dense(torch.from_numpy(x).cuda().to(torch.bfloat16), wr, quant(t), torch.from_numpy(bias).cuda())
+    refb = oracle.dense(int(t), w, torch.from_numpy(x).to(torch.bfloat16).float().numpy(), bias, 0, route="f64")
+    assert rel_err(yb.cpu().numpy(), refb) <= 2e-4
+    wr.free()
+
+
+@pytest.mark.parametrize("name", ["Q4_K", "Q6_K"])
+def test_integer_path_activation_edge_cases(oracle, force_integer_path, name):
+    """Sub-blocks of zeros, a large outlier, values beyond the fp16 range (clamped like the fp16 path) and
+    activations that differ by orders of magnitude between sub-blocks."""
+    t = TYPES[name]
+    n, k = 48, 1024
+    w = oracle.make_weights(int(t), n, k, seed=77)
+    rng = np.random.default_rng(78)
+    x = rng.standard_normal((1, k)).astype(np.float32)
+    x[0, 0:64] = 0.0
+    x[0, 100] = 3000.0
+    x[0, 256:288] *= 1e-6
+    x[0, 512:544] *= 1e3
+    ref = oracle.dense(int(t), w, x, route="f64")
+    y = g.quantized_dense(torch.from_numpy(x).cuda(), w, quant(t))
+    assert rel_err(y.cpu().numpy(), ref) <= 5e-4
+    x[0, 700] = 1e6   # beyond 65504: both paths saturate
+    xs = np.clip(x, -65504.0, 65504.0)
+    y = g.quantized_dense(torch.from_numpy(x).cuda(), w, quant(t))
+    assert np.isfinite(y.cpu().numpy()).all()
+    assert rel_err(y.cpu().numpy(), oracle.dense(int(t), w, xs, route="f64")) <= 5e-4
+
+
+def test_integer_path_batched_segments(oracle, force_integer_path):
+    """q+k style launch (two matrices, one x) through the integer path equals the separate launches."""
+    t = g.GGMLQuantType.Q4_K
+    k = 2048
+    ws = [g.upload(oracle.make_weights(12, n, k, seed=n), t) for n in (528, 130)]
+    x = torch.from_numpy(np.random.default_rng(1).standard_normal((1, k)).astype(np.float32)).cuda()
+    outs = g.backend_fused_quantized_dense_batch(x, ws, None, quant(t), [g.ActivationType.SILU, g.ActivationType.NONE])
+    for w, y, a in zip(ws, outs, (g.ActivationType.SILU, g.ActivationType.NONE)):
+        want = g.backend_fused_quantized_dense(x, w, None, quant(t), a)
+        assert float((y - want).abs().max()) <= 1e-5 * max(1.0, float(want.abs().max()))
+        w.free()
+
+
 # ----------------------------------------------------------------------------- BASELINE shapes
 @pytest.mark.parametrize("name,n,k,sigma,ms", [
     ("Q8_0", 4096, 4096, 0.02, [1]),                 # configs[0]
