@@ -661,7 +661,7 @@ __device__ __forceinline__ void imma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1,
 template <int TYPE>
 __device__ __forceinline__ void stage_x_i8(const GemvParams &p, int64_t k0, int kc, uint8_t *dig, float *sx, float *xsum) {
     constexpr int BLK = I8Fmt<TYPE>::BLK, TPB = BLK / 8;  // threads per sub-block
-    const size_t L = dig_array_bytes<TYPE>(kc >> 8);
+    const size_t L = dig_array_bytes<TYPE>(p.kts);  // array size of a full K slice, also where this slice is shorter
     uint8_t *hi = dig, *lo = dig + L + I8Fmt<TYPE>::LO, *zero = dig + 2 * L + 2 * I8Fmt<TYPE>::LO;
     const int gpc = kc >> 3;
     for (int gi = threadIdx.x; gi < gpc; gi += blockDim.x) {
@@ -757,6 +757,63 @@ __device__ __forceinline__ void tile_q4_k_i8(uint32_t tile, int lane, uint32_t d
     yg8 += (ds_lo8 * sl) * (float)(128 * cl[2] + cl[3]) - dm_lo8 * xl + (ds_hi8 * sh) * (float)(128 * ch[2] + ch[3]) - dm_hi8 * xh;
 }
 
+__device__ __forceinline__ void imma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// One 16 x 256 Q4_0 tile, integer path.  The lane's quarter holds blocks 2t, 2t+1 (32 values, one fp16 scale
+// each); low nibbles are elements 0..15 of a block, high nibbles elements 16..31 (ml/ggml/dequant.go:83-115).
+//     y_row += d * (s * S - 8 * s * sum(xq))     per block
+__device__ __forceinline__ void tile_q4_0_i8(uint32_t tile, int lane, uint32_t dig, uint32_t sxp, uint32_t xsp, float &yg, float &yg8) {
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t sc = lds32(tile + g * 16 + t * 4), sc8 = lds32(tile + (g + 8) * 16 + t * 4);
+    const uint2 s2 = lds64(sxp), x2 = lds64(xsp);
+    constexpr uint32_t M = 0x0F0F0F0Fu;
+#pragma unroll
+    for (int bp = 0; bp < 2; bp++) {
+        const uint4 qa = lds128(tile + 256 + (2 * bp) * 512 + lane * 16);
+        const uint4 qb = lds128(tile + 256 + (2 * bp + 1) * 512 + lane * 16);
+        const uint4 dl = lds128(dig + 32 * bp), dh = lds128(dig + 32 * bp + 16);
+        int c[4] = {0, 0, 0, 0};
+        imma_u8s8(c, qa.x & M, qb.x & M, qa.y & M, qb.y & M, dl.x, dl.y);
+        imma_u8s8(c, qa.z & M, qb.z & M, qa.w & M, qb.w & M, dl.z, dl.w);
+        imma_u8s8(c, (qa.x >> 4) & M, (qb.x >> 4) & M, (qa.y >> 4) & M, (qb.y >> 4) & M, dh.x, dh.y);
+        imma_u8s8(c, (qa.z >> 4) & M, (qb.z >> 4) & M, (qa.w >> 4) & M, (qb.w >> 4) & M, dh.z, dh.w);
+        const float d = __half2float(__ushort_as_half((unsigned short)(bp ? sc >> 16 : sc & 0xFFFFu)));
+        const float d8 = __half2float(__ushort_as_half((unsigned short)(bp ? sc8 >> 16 : sc8 & 0xFFFFu)));
+        const float sb = __uint_as_float(bp ? s2.y : s2.x), xb = __uint_as_float(bp ? x2.y : x2.x);
+        yg += d * (sb * (float)(128 * c[0] + c[1]) - 8.0f * xb);
+        yg8 += d8 * (sb * (float)(128 * c[2] + c[3]) - 8.0f * xb);
+    }
+}
+
+// One 16 x 256 Q8_0 tile, integer path: the int8 codes are the MMA operand as stored (ml/ggml/dequant.go:58-78).
+__device__ __forceinline__ void tile_q8_0_i8(uint32_t tile, int lane, uint32_t dig, uint32_t sxp, uint32_t xsp, float &yg, float &yg8) {
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t sc = lds32(tile + g * 16 + t * 4), sc8 = lds32(tile + (g + 8) * 16 + t * 4);
+    const uint2 s2 = lds64(sxp);
+    (void)xsp;
+#pragma unroll
+    for (int bp = 0; bp < 2; bp++) {
+        int c[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint4 qa = lds128(tile + 256 + (2 * (2 * bp + h)) * 512 + lane * 16);
+            const uint4 qb = lds128(tile + 256 + (2 * (2 * bp + h) + 1) * 512 + lane * 16);
+            const uint4 dg = lds128(dig + 32 * bp + 16 * h);
+            imma_s8s8(c, qa.x, qb.x, qa.y, qb.y, dg.x, dg.y);
+            imma_s8s8(c, qa.z, qb.z, qa.w, qb.w, dg.z, dg.w);
+        }
+        const float d = __half2float(__ushort_as_half((unsigned short)(bp ? sc >> 16 : sc & 0xFFFFu)));
+        const float d8 = __half2float(__ushort_as_half((unsigned short)(bp ? sc8 >> 16 : sc8 & 0xFFFFu)));
+        const float sb = __uint_as_float(bp ? s2.y : s2.x);
+        yg += (d * sb) * (float)(128 * c[0] + c[1]);
+        yg8 += (d8 * sb) * (float)(128 * c[2] + c[3]);
+    }
+}
+
 // d * scale of the lane's four sub-blocks (8n + lh + 2c, c = 0..3) of one Q6_K row, in f32.
 __device__ __forceinline__ void q6k_scales_f32(const uint2 &s, int lh, float d, float (&ds)[4]) {
     const uint32_t lo = lh ? s.x >> 8 : s.x, hi = lh ? s.y >> 8 : s.y;  // bytes 0 and 2: scales of c = 0, 1 | 2, 3
@@ -823,7 +880,7 @@ __device__ __forceinline__ int segment_of(const GemvParams &p, int rt) {
 // Shared memory: staged x | aux sums | partial sums per unit | tile rings | mbarriers.
 template <int TYPE, int NB, bool I8>
 __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
-    static_assert(!I8 || ((TYPE == kQ4_K || TYPE == kQ6_K) && NB == 1), "the integer path exists for Q4_K and Q6_K at m = 1");
+    static_assert(!I8 || NB == 1, "the integer path exists at m = 1");
     using IF = I8Fmt<TYPE>;
     using F = Fmt<TYPE>;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -932,8 +989,8 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
     if constexpr (I8) {
         const uint32_t L = (uint32_t)dig_array_bytes<TYPE>(p.kts), base = smem_u32(smem);
         // offset of the lane's values inside a tile, and of its first sub-block's scale
-        const int voff = TYPE == kQ4_K ? 64 * t + IF::PAD * (t >> 1) : 128 * (t >> 1) + 16 * (t & 1) + IF::PAD * (t >> 1);
-        const int soff = TYPE == kQ4_K ? 8 * t : 4 * (8 * (t >> 1) + (t & 1));
+        const int voff = TYPE != kQ6_K ? 64 * t + IF::PAD * (t >> 1) : 128 * (t >> 1) + 16 * (t & 1) + IF::PAD * (t >> 1);
+        const int soff = TYPE != kQ6_K ? 8 * t : 4 * (8 * (t >> 1) + (t & 1));
         dig_lane = g == 2 * t ? base + voff : g == 2 * t + 1 ? base + L + IF::LO + voff : base + 2 * L + 2 * IF::LO;
         sx_lane = smem_u32(sx) + soff, xs_lane = smem_u32(xsum) + soff;
     }
@@ -1013,8 +1070,12 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
                 if constexpr (I8) {
                     if constexpr (TYPE == kQ4_K) {
                         tile_q4_k_i8(tile, lane, dig, sxp, xsp, yg, yg8);
-                    } else {
+                    } else if constexpr (TYPE == kQ6_K) {
                         tile_q6_k_i8(tile, lane, dig, sxp, xsp, yg, yg8);
+                    } else if constexpr (TYPE == kQ4_0) {
+                        tile_q4_0_i8(tile, lane, dig, sxp, xsp, yg, yg8);
+                    } else {
+                        tile_q8_0_i8(tile, lane, dig, sxp, xsp, yg, yg8);
                     }
                     dig += kDigTile, sxp += kScaleTile, xsp += kScaleTile;
                 } else if constexpr (TYPE == kQ4_0) {
@@ -1258,7 +1319,7 @@ int launch_t(const Weight &w, const GemvParams &p0, cudaStream_t s) {
 
 template <int TYPE>
 int launch_nb(const Weight &w, const GemvParams &p, cudaStream_t s) {
-    if constexpr (TYPE == kQ4_K || TYPE == kQ6_K) {
+    {
         // m = 1: integer tensor-core path (B200Q_GEMV_I8=0 selects the fp16 path, for comparisons)
         // Quantizing the activations costs every CTA more than staging them as fp16 (measured: about 1.5 us
         // per launch against 0.034 us saved per tile and SM), so the path pays from about 44 tiles per SM.

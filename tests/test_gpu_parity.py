@@ -309,8 +309,8 @@ def force_integer_path(monkeypatch):
     monkeypatch.setenv("B200Q_GEMV_I8", "2")
 
 
-@pytest.mark.parametrize("name", ["Q4_K", "Q6_K"])
-@pytest.mark.parametrize("n,k", [(16, 256), (100, 512), (1000, 2048), (272, 4096), (64, 14336)])
+@pytest.mark.parametrize("name", ["Q4_K", "Q6_K", "Q4_0", "Q8_0"])
+@pytest.mark.parametrize("n,k", [(16, 256), (100, 512), (1000, 2048), (272, 4096), (64, 14336), (32, 1280), (48, 2816)])
 def test_integer_path_parity(oracle, force_integer_path, name, n, k):
     t = TYPES[name]
     w = oracle.make_weights(int(t), n, k, seed=n + k)
@@ -329,7 +329,19 @@ def test_integer_path_parity(oracle, force_integer_path, name, n, k):
     wr.free()
 
 
-@pytest.mark.parametrize("name", ["Q4_K", "Q6_K"])
+@pytest.mark.parametrize("name", ["Q4_0", "Q8_0"])
+def test_integer_path_ragged_k(oracle, force_integer_path, name):
+    """K = 41 blocks of 32: the last 256-value tile is partly padding."""
+    t = TYPES[name]
+    n, k = 130, 1312
+    w = oracle.make_weights(int(t), n, k, seed=8)
+    x = np.random.default_rng(9).standard_normal((1, k)).astype(np.float32)
+    ref = oracle.dense(int(t), w, x, route="f64")
+    y = g.quantized_dense(torch.from_numpy(x).cuda(), w, quant(t))
+    assert rel_err(y.cpu().numpy(), ref) <= 2e-4
+
+
+@pytest.mark.parametrize("name", ["Q4_K", "Q6_K", "Q4_0", "Q8_0"])
 def test_integer_path_activation_edge_cases(oracle, force_integer_path, name):
     """Sub-blocks of zeros, a large outlier, values beyond the fp16 range (clamped like the fp16 path) and
     activations that differ by orders of magnitude between sub-blocks."""
