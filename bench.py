@@ -356,7 +356,7 @@ def run_cuda(args) -> None:
         "peak_source": pk["source"], "us_per_launch": gu_us, "bytes_per_launch": gu_bytes,
         # dram__bytes_read + dram__bytes_write per launch: ncu measured 33.10 MB for the 33.03 MB launch
         # at N = 1 (profiles/gemv_q4k_14336x4096_m1.md); traffic grows in proportion to the rows a rank holds
-        "traffic": args.traffic if args.traffic is not None else gu_bytes * (33104640.0 / 33030144.0),
+        "traffic": args.traffic if args.traffic is not None else gu_bytes * (33089792.0 / 33030144.0),
         "traffic_source": "ncu capture of the N=1 launch, scaled by bytes per launch",
     }
 
