@@ -80,8 +80,8 @@ class PeerScatterBuffers:
     """One symmetric-memory buffer per rank, mapped into every rank of ``group`` (CUDA peer memory over
     NVLink), for layers whose kernels write their output slice straight into all peers.
 
-    Allocate ONE instance per process group and carve the regions of all layers out of it: a second
-    allocation in the same process did not get through its first rendezvous barrier on a 2-GPU box.
+    Allocate one instance per process group and carve the regions of all layers out of it (one rendezvous,
+    one set of sync words).
 
     ``floats`` float32 values are allocated on every rank; ``ptr(rank, offset)`` is the device address,
     in this process, of element ``offset`` of ``rank``'s buffer, and ``local`` is this rank's buffer as a
