@@ -1244,8 +1244,9 @@ int launch_t(const Weight &w, const GemvParams &p0, cudaStream_t s) {
 
     // Two CTAs of up to 8 warps per SM (half the shared memory each) when the staged activations are
     // small: finer load balance, and a dependent launch can move into an SM as soon as one CTA leaves.
-    const size_t x_per_ktile = I8 ? (size_t)(3 * (256 + I8Fmt<TYPE>::PAD) + 2 * 4 * (256 / I8Fmt<TYPE>::BLK) + 16)
-                                  : (size_t)p.m * (F::TK * 2 + (F::SUB ? 4 * (F::TK / F::SUB) : 0));
+    // Staged bytes per k tile as the planner's cost model knows them (calibrated on the fp16 staging; the
+    // integer path stages 1.6x the bytes in the same time, and its true size enters the budget further down).
+    const size_t x_per_ktile = (size_t)p.m * (F::TK * 2 + (F::SUB ? 4 * (F::TK / F::SUB) : 0));
     const size_t x_whole = x_per_ktile * (size_t)w.kt;
     int cps = 1;
     (void)x_whole;
@@ -1321,11 +1322,11 @@ template <int TYPE>
 int launch_nb(const Weight &w, const GemvParams &p, cudaStream_t s) {
     {
         // m = 1: integer tensor-core path (B200Q_GEMV_I8=0 selects the fp16 path, for comparisons)
-        // Quantizing the activations costs every CTA more than staging them as fp16 (measured: about 1.5 us
-        // per launch against 0.034 us saved per tile and SM), so the path pays from about 44 tiles per SM.
+        // Measured faster than the fp16 path from the smallest decoder matrices (1024 x 4096) up, so the size
+        // threshold defaults to none.
         // (read at every launch so that tests can force either path: 0 = never, 1 = by size, 2 = always)
         const int i8 = env_int("B200Q_GEMV_I8", 1);
-        const int i8_min_tiles = env_int("B200Q_GEMV_I8_MIN_TILES", 44);
+        const int i8_min_tiles = env_int("B200Q_GEMV_I8_MIN_TILES", 0);
         if (i8 != 0 && p.m == 1 && (i8 == 2 || w.rt * w.kt >= (int64_t)i8_min_tiles * 148)) return launch_t<TYPE, 1, true>(w, p, s);
     }
     return p.m <= 8 ? launch_t<TYPE, 1, false>(w, p, s) : launch_t<TYPE, 2, false>(w, p, s);
