@@ -363,7 +363,7 @@ def run_cuda(args) -> None:
     out = {
         "metric": "decode_weight_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": ("u4/u6 codes x 15-bit activations in int8 tensor-core MMAs (s32), block scales in f32; f16 MMA / f32 accumulate for small matrices and batch > 1" if batch == 1 else "f16 multiply / f32 accumulate on packed u8 blocks"), "data": "synthetic",
+        "vs_baseline": None, "dtype": ("u4/u6 codes x 15-bit activations in int8 tensor-core MMAs (s32), block scales in f32" if batch == 1 else "f16 multiply / f32 accumulate on packed u8 blocks"), "data": "synthetic",
         "config": {"workload": WORKLOAD, "batch": batch, "weight_bytes_per_step": total_bytes,
                    "parallelism": f"rows/{world}" + {"none": "", "nccl": " + NCCL all-gather per projection",
                                                            "peer": " + all-gather fused into the GEMV epilogue (NVLink peer stores), " +

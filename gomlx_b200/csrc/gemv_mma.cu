@@ -35,7 +35,7 @@
 // rounded to fp16 after scaling (block scales must stay below 64 in magnitude).
 // Accumulation is f32.  Relative to the f32 reference this costs below 1e-3 of the output scale.
 //
-// For m = 1 and matrices large enough to pay for it, Q4_K and Q6_K take an integer path instead (see
+// For m = 1 every format takes an integer path instead (see
 // "Integer path" below): the packed codes enter m16n8k32 integer MMAs unscaled, the activations as
 // two int8 digits of a 15-bit fixed-point number per sub-block, and the block scales are applied in f32
 // to the exact integer dot products.  It needs about a third fewer ALU-pipe instructions per tile (the
