@@ -659,7 +659,7 @@ __device__ __forceinline__ void imma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1,
 // Quantizes x[k0 .. k0+kc) of one batch row into the digit arrays (see above).  A thread handles 8
 // values, BLK / 8 neighbouring threads one sub-block.
 template <int TYPE>
-__device__ __forceinline__ void stage_x_i8(const GemvParams &p, int64_t k0, int kc, uint8_t *dig, float *sx, float *xsum) {
+__device__ __forceinline__ void stage_x_i8(const GemvParams &p, int row, int64_t k0, int kc, uint8_t *dig, float *sx, float *xsum) {
     constexpr int BLK = I8Fmt<TYPE>::BLK, TPB = BLK / 8;  // threads per sub-block
     const size_t L = dig_array_bytes<TYPE>(p.kts);  // array size of a full K slice, also where this slice is shorter
     uint8_t *hi = dig, *lo = dig + L + I8Fmt<TYPE>::LO, *zero = dig + 2 * L + 2 * I8Fmt<TYPE>::LO;
@@ -667,13 +667,13 @@ __device__ __forceinline__ void stage_x_i8(const GemvParams &p, int64_t k0, int 
     for (int gi = threadIdx.x; gi < gpc; gi += blockDim.x) {
         const int64_t k = k0 + (int64_t)gi * 8;
         float v[8];
-        if (k < p.k) {
+        if (k < p.k && row < p.m) {  // batch rows beyond m (padding of the row group) are zeros
             if (p.x_dtype == B200Q_F32) {
-                const float4 *src = reinterpret_cast<const float4 *>(static_cast<const float *>(p.x) + k);
+                const float4 *src = reinterpret_cast<const float4 *>(static_cast<const float *>(p.x) + (int64_t)row * p.k + k);
                 const float4 a = __ldg(src), b = __ldg(src + 1);
                 v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
             } else {
-                const uint4 r = __ldg(reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.x) + k));
+                const uint4 r = __ldg(reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.x) + (int64_t)row * p.k + k));
                 const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
                 for (int i = 0; i < 4; i++) v[2 * i] = __uint_as_float(w[i] << 16), v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
@@ -732,29 +732,44 @@ __device__ __forceinline__ void q4k_scales_f32(const uint4 &h, int t, float &ds_
     dm_lo = dmin * (float)(mn2 & 0xFFu), dm_hi = dmin * (float)(mn2 >> 8);
 }
 
-// One 16 x 256 Q4_K tile, integer path.  dig: this lane's digit array at the tile's quarter t (or the zero
-// array); sxp / xsp: shared-memory addresses of s and s*sum(xq) of the tile's sub-blocks 2t, 2t+1.
-__device__ __forceinline__ void tile_q4_k_i8(uint32_t tile, int lane, uint32_t dig, uint32_t sxp, uint32_t xsp, float &yg, float &yg8) {
+// Integer-path tile functions.  MI = batch rows (1 or 2): the codes are unpacked once and multiplied with
+// every batch row's digits (row r's digit arrays lie dstride bytes, its scales sstride bytes after row 0's).
+// dig: this lane's digit array at the lane's first value of the tile (or the zero array); sxp / xsp:
+// shared-memory addresses of s and s*sum(xq) of the lane's first sub-block of the tile.
+
+// One 16 x 256 Q4_K tile: the lane's quarter t holds sub-blocks 2t (low nibbles) and 2t+1 (high nibbles).
+template <int MI>
+__device__ __forceinline__ void tile_q4_k_i8(uint32_t tile, int lane, uint32_t dig, uint32_t sxp, uint32_t xsp, uint32_t dstride,
+                                             uint32_t sstride, float (&yg)[MI], float (&yg8)[MI]) {
     const int g = lane >> 2, t = lane & 3;
     float ds_lo, ds_hi, dm_lo, dm_hi, ds_lo8, ds_hi8, dm_lo8, dm_hi8;
     q4k_scales_f32(lds128(tile + g * 16), t, ds_lo, ds_hi, dm_lo, dm_hi);
     q4k_scales_f32(lds128(tile + (g + 8) * 16), t, ds_lo8, ds_hi8, dm_lo8, dm_hi8);
-    int cl[4] = {0, 0, 0, 0}, ch[4] = {0, 0, 0, 0};  // (row g: hi, lo digit), (row g+8: hi, lo digit)
+    int cl[MI][4] = {}, ch[MI][4] = {};  // (row g: hi, lo digit), (row g+8: hi, lo digit)
     constexpr uint32_t M = 0x0F0F0F0Fu;
 #pragma unroll
     for (int i = 0; i < 2; i++) {
         const uint4 qa = lds128(tile + 256 + (2 * i) * 512 + lane * 16);
         const uint4 qb = lds128(tile + 256 + (2 * i + 1) * 512 + lane * 16);
-        const uint4 dl = lds128(dig + 16 * i), dh = lds128(dig + 32 + 16 * i);
-        imma_u8s8(cl, qa.x & M, qb.x & M, qa.y & M, qb.y & M, dl.x, dl.y);
-        imma_u8s8(cl, qa.z & M, qb.z & M, qa.w & M, qb.w & M, dl.z, dl.w);
-        imma_u8s8(ch, (qa.x >> 4) & M, (qb.x >> 4) & M, (qa.y >> 4) & M, (qb.y >> 4) & M, dh.x, dh.y);
-        imma_u8s8(ch, (qa.z >> 4) & M, (qb.z >> 4) & M, (qa.w >> 4) & M, (qb.w >> 4) & M, dh.z, dh.w);
+        const uint32_t la[4] = {qa.x & M, qa.y & M, qa.z & M, qa.w & M}, lb[4] = {qb.x & M, qb.y & M, qb.z & M, qb.w & M};
+        const uint32_t ha[4] = {(qa.x >> 4) & M, (qa.y >> 4) & M, (qa.z >> 4) & M, (qa.w >> 4) & M};
+        const uint32_t hb[4] = {(qb.x >> 4) & M, (qb.y >> 4) & M, (qb.z >> 4) & M, (qb.w >> 4) & M};
+#pragma unroll
+        for (int r = 0; r < MI; r++) {
+            const uint4 dl = lds128(dig + r * dstride + 16 * i), dh = lds128(dig + r * dstride + 32 + 16 * i);
+            imma_u8s8(cl[r], la[0], lb[0], la[1], lb[1], dl.x, dl.y);
+            imma_u8s8(cl[r], la[2], lb[2], la[3], lb[3], dl.z, dl.w);
+            imma_u8s8(ch[r], ha[0], hb[0], ha[1], hb[1], dh.x, dh.y);
+            imma_u8s8(ch[r], ha[2], hb[2], ha[3], hb[3], dh.z, dh.w);
+        }
     }
-    const uint2 s2 = lds64(sxp), x2 = lds64(xsp);
-    const float sl = __uint_as_float(s2.x), sh = __uint_as_float(s2.y), xl = __uint_as_float(x2.x), xh = __uint_as_float(x2.y);
-    yg += (ds_lo * sl) * (float)(128 * cl[0] + cl[1]) - dm_lo * xl + (ds_hi * sh) * (float)(128 * ch[0] + ch[1]) - dm_hi * xh;
-    yg8 += (ds_lo8 * sl) * (float)(128 * cl[2] + cl[3]) - dm_lo8 * xl + (ds_hi8 * sh) * (float)(128 * ch[2] + ch[3]) - dm_hi8 * xh;
+#pragma unroll
+    for (int r = 0; r < MI; r++) {
+        const uint2 s2 = lds64(sxp + r * sstride), x2 = lds64(xsp + r * sstride);
+        const float sl = __uint_as_float(s2.x), sh = __uint_as_float(s2.y), xl = __uint_as_float(x2.x), xh = __uint_as_float(x2.y);
+        yg[r] += (ds_lo * sl) * (float)(128 * cl[r][0] + cl[r][1]) - dm_lo * xl + (ds_hi * sh) * (float)(128 * ch[r][0] + ch[r][1]) - dm_hi * xh;
+        yg8[r] += (ds_lo8 * sl) * (float)(128 * cl[r][2] + cl[r][3]) - dm_lo8 * xl + (ds_hi8 * sh) * (float)(128 * ch[r][2] + ch[r][3]) - dm_hi8 * xh;
+    }
 }
 
 __device__ __forceinline__ void imma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -763,54 +778,68 @@ __device__ __forceinline__ void imma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1,
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// One 16 x 256 Q4_0 tile, integer path.  The lane's quarter holds blocks 2t, 2t+1 (32 values, one fp16 scale
-// each); low nibbles are elements 0..15 of a block, high nibbles elements 16..31 (ml/ggml/dequant.go:83-115).
+// One 16 x 256 Q4_0 tile.  The lane's quarter holds blocks 2t, 2t+1 (32 values, one fp16 scale each); low
+// nibbles are elements 0..15 of a block, high nibbles elements 16..31 (ml/ggml/dequant.go:83-115).
 //     y_row += d * (s * S - 8 * s * sum(xq))     per block
-__device__ __forceinline__ void tile_q4_0_i8(uint32_t tile, int lane, uint32_t dig, uint32_t sxp, uint32_t xsp, float &yg, float &yg8) {
+template <int MI>
+__device__ __forceinline__ void tile_q4_0_i8(uint32_t tile, int lane, uint32_t dig, uint32_t sxp, uint32_t xsp, uint32_t dstride,
+                                             uint32_t sstride, float (&yg)[MI], float (&yg8)[MI]) {
     const int g = lane >> 2, t = lane & 3;
     const uint32_t sc = lds32(tile + g * 16 + t * 4), sc8 = lds32(tile + (g + 8) * 16 + t * 4);
-    const uint2 s2 = lds64(sxp), x2 = lds64(xsp);
     constexpr uint32_t M = 0x0F0F0F0Fu;
 #pragma unroll
     for (int bp = 0; bp < 2; bp++) {
         const uint4 qa = lds128(tile + 256 + (2 * bp) * 512 + lane * 16);
         const uint4 qb = lds128(tile + 256 + (2 * bp + 1) * 512 + lane * 16);
-        const uint4 dl = lds128(dig + 32 * bp), dh = lds128(dig + 32 * bp + 16);
-        int c[4] = {0, 0, 0, 0};
-        imma_u8s8(c, qa.x & M, qb.x & M, qa.y & M, qb.y & M, dl.x, dl.y);
-        imma_u8s8(c, qa.z & M, qb.z & M, qa.w & M, qb.w & M, dl.z, dl.w);
-        imma_u8s8(c, (qa.x >> 4) & M, (qb.x >> 4) & M, (qa.y >> 4) & M, (qb.y >> 4) & M, dh.x, dh.y);
-        imma_u8s8(c, (qa.z >> 4) & M, (qb.z >> 4) & M, (qa.w >> 4) & M, (qb.w >> 4) & M, dh.z, dh.w);
+        const uint32_t la[4] = {qa.x & M, qa.y & M, qa.z & M, qa.w & M}, lb[4] = {qb.x & M, qb.y & M, qb.z & M, qb.w & M};
+        const uint32_t ha[4] = {(qa.x >> 4) & M, (qa.y >> 4) & M, (qa.z >> 4) & M, (qa.w >> 4) & M};
+        const uint32_t hb[4] = {(qb.x >> 4) & M, (qb.y >> 4) & M, (qb.z >> 4) & M, (qb.w >> 4) & M};
         const float d = __half2float(__ushort_as_half((unsigned short)(bp ? sc >> 16 : sc & 0xFFFFu)));
         const float d8 = __half2float(__ushort_as_half((unsigned short)(bp ? sc8 >> 16 : sc8 & 0xFFFFu)));
-        const float sb = __uint_as_float(bp ? s2.y : s2.x), xb = __uint_as_float(bp ? x2.y : x2.x);
-        yg += d * (sb * (float)(128 * c[0] + c[1]) - 8.0f * xb);
-        yg8 += d8 * (sb * (float)(128 * c[2] + c[3]) - 8.0f * xb);
+#pragma unroll
+        for (int r = 0; r < MI; r++) {
+            const uint4 dl = lds128(dig + r * dstride + 32 * bp), dh = lds128(dig + r * dstride + 32 * bp + 16);
+            int c[4] = {0, 0, 0, 0};
+            imma_u8s8(c, la[0], lb[0], la[1], lb[1], dl.x, dl.y);
+            imma_u8s8(c, la[2], lb[2], la[3], lb[3], dl.z, dl.w);
+            imma_u8s8(c, ha[0], hb[0], ha[1], hb[1], dh.x, dh.y);
+            imma_u8s8(c, ha[2], hb[2], ha[3], hb[3], dh.z, dh.w);
+            const float sb = __uint_as_float(lds32(sxp + r * sstride + 4 * bp)), xb = __uint_as_float(lds32(xsp + r * sstride + 4 * bp));
+            yg[r] += d * (sb * (float)(128 * c[0] + c[1]) - 8.0f * xb);
+            yg8[r] += d8 * (sb * (float)(128 * c[2] + c[3]) - 8.0f * xb);
+        }
     }
 }
 
-// One 16 x 256 Q8_0 tile, integer path: the int8 codes are the MMA operand as stored (ml/ggml/dequant.go:58-78).
-__device__ __forceinline__ void tile_q8_0_i8(uint32_t tile, int lane, uint32_t dig, uint32_t sxp, uint32_t xsp, float &yg, float &yg8) {
+// One 16 x 256 Q8_0 tile: the int8 codes are the MMA operand as stored (ml/ggml/dequant.go:58-78).
+template <int MI>
+__device__ __forceinline__ void tile_q8_0_i8(uint32_t tile, int lane, uint32_t dig, uint32_t sxp, uint32_t xsp, uint32_t dstride,
+                                             uint32_t sstride, float (&yg)[MI], float (&yg8)[MI]) {
     const int g = lane >> 2, t = lane & 3;
     const uint32_t sc = lds32(tile + g * 16 + t * 4), sc8 = lds32(tile + (g + 8) * 16 + t * 4);
-    const uint2 s2 = lds64(sxp);
     (void)xsp;
 #pragma unroll
     for (int bp = 0; bp < 2; bp++) {
-        int c[4] = {0, 0, 0, 0};
+        int c[MI][4] = {};
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const uint4 qa = lds128(tile + 256 + (2 * (2 * bp + h)) * 512 + lane * 16);
             const uint4 qb = lds128(tile + 256 + (2 * (2 * bp + h) + 1) * 512 + lane * 16);
-            const uint4 dg = lds128(dig + 32 * bp + 16 * h);
-            imma_s8s8(c, qa.x, qb.x, qa.y, qb.y, dg.x, dg.y);
-            imma_s8s8(c, qa.z, qb.z, qa.w, qb.w, dg.z, dg.w);
+#pragma unroll
+            for (int r = 0; r < MI; r++) {
+                const uint4 dg = lds128(dig + r * dstride + 32 * bp + 16 * h);
+                imma_s8s8(c[r], qa.x, qb.x, qa.y, qb.y, dg.x, dg.y);
+                imma_s8s8(c[r], qa.z, qb.z, qa.w, qb.w, dg.z, dg.w);
+            }
         }
         const float d = __half2float(__ushort_as_half((unsigned short)(bp ? sc >> 16 : sc & 0xFFFFu)));
         const float d8 = __half2float(__ushort_as_half((unsigned short)(bp ? sc8 >> 16 : sc8 & 0xFFFFu)));
-        const float sb = __uint_as_float(bp ? s2.y : s2.x);
-        yg += (d * sb) * (float)(128 * c[0] + c[1]);
-        yg8 += (d8 * sb) * (float)(128 * c[2] + c[3]);
+#pragma unroll
+        for (int r = 0; r < MI; r++) {
+            const float sb = __uint_as_float(lds32(sxp + r * sstride + 4 * bp));
+            yg[r] += (d * sb) * (float)(128 * c[r][0] + c[r][1]);
+            yg8[r] += (d8 * sb) * (float)(128 * c[r][2] + c[r][3]);
+        }
     }
 }
 
@@ -821,10 +850,11 @@ __device__ __forceinline__ void q6k_scales_f32(const uint2 &s, int lh, float d, 
     ds[2] = d * (float)(int)(int8_t)(hi & 0xFFu), ds[3] = d * (float)(int)(int8_t)((hi >> 16) & 0xFFu);
 }
 
-// One 16 x 256 Q6_K tile, integer path.  Lane t = 2n + lh owns values 128n + 32c + 16lh + 0..15, c = 0..3, of
-// rows g and g+8: four 16-value sub-blocks, each two integer MMAs.  dig: the lane's digit array at the tile's
-// offset 128n + 16lh (+ padding); sxp / xsp: s and s*sum(xq) of sub-block 8n + lh (the others 2c further).
-__device__ __forceinline__ void tile_q6_k_i8(uint32_t tile, int lane, uint32_t dig, uint32_t sxp, uint32_t xsp, float &yg, float &yg8) {
+// One 16 x 256 Q6_K tile.  Lane t = 2n + lh owns values 128n + 32c + 16lh + 0..15, c = 0..3, of rows g and g+8:
+// four 16-value sub-blocks, each two integer MMAs.  The scales of sub-block c lie 2c entries after the first.
+template <int MI>
+__device__ __forceinline__ void tile_q6_k_i8(uint32_t tile, int lane, uint32_t dig, uint32_t sxp, uint32_t xsp, uint32_t dstride,
+                                             uint32_t sstride, float (&yg)[MI], float (&yg8)[MI]) {
     const int g = lane >> 2, t = lane & 3, n = t >> 1, lh = t & 1;
     const float dg = __half2float(__ushort_as_half((unsigned short)lds16(tile + 3328 + g * 2)));
     const float dg8 = __half2float(__ushort_as_half((unsigned short)lds16(tile + 3328 + (g + 8) * 2)));
@@ -834,11 +864,8 @@ __device__ __forceinline__ void tile_q6_k_i8(uint32_t tile, int lane, uint32_t d
     const uint4 la = lds128(tile + 256 + 0 * 512 + lane * 16), la8 = lds128(tile + 256 + 1 * 512 + lane * 16);
     const uint4 lb = lds128(tile + 256 + 2 * 512 + lane * 16), lb8 = lds128(tile + 256 + 3 * 512 + lane * 16);
     const uint4 hh = lds128(tile + 256 + 4 * 512 + lane * 16), hh8 = lds128(tile + 256 + 5 * 512 + lane * 16);
-    int acc[4][4] = {};  // [c][(row g: hi, lo digit), (row g+8: hi, lo digit)]
+    int acc[MI][4][4] = {};  // [batch row][c][(row g: hi, lo digit), (row g+8: hi, lo digit)]
     constexpr uint32_t ML = 0x0F0F0F0Fu, MH = 0x30303030u;
-    uint4 dgt[4];
-#pragma unroll
-    for (int c = 0; c < 4; c++) dgt[c] = lds128(dig + 32 * c);
 #pragma unroll
     for (int half = 0; half < 2; half++) {  // words (0, 1) then (2, 3) of every 16-byte piece
         uint32_t code[2][4], code8[2][4];
@@ -854,15 +881,22 @@ __device__ __forceinline__ void tile_q6_k_i8(uint32_t tile, int lane, uint32_t d
             code8[w2][2] = ((a8 >> 4) & ML) | (h8 & MH), code8[w2][3] = ((bq8 >> 4) & ML) | ((h8 >> 2) & MH);
         }
 #pragma unroll
-        for (int c = 0; c < 4; c++)
-            imma_u8s8(acc[c], code[0][c], code8[0][c], code[1][c], code8[1][c], half == 0 ? dgt[c].x : dgt[c].z,
-                      half == 0 ? dgt[c].y : dgt[c].w);
+        for (int r = 0; r < MI; r++) {
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const uint2 dgt = lds64(dig + r * dstride + 32 * c + 8 * half);
+                imma_u8s8(acc[r][c], code[0][c], code8[0][c], code[1][c], code8[1][c], dgt.x, dgt.y);
+            }
+        }
     }
 #pragma unroll
-    for (int c = 0; c < 4; c++) {
-        const float sc = __uint_as_float(lds32(sxp + 8 * c)), xs = __uint_as_float(lds32(xsp + 8 * c));
-        yg += ds[c] * (sc * (float)(128 * acc[c][0] + acc[c][1]) - 32.0f * xs);
-        yg8 += ds8[c] * (sc * (float)(128 * acc[c][2] + acc[c][3]) - 32.0f * xs);
+    for (int r = 0; r < MI; r++) {
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const float sc = __uint_as_float(lds32(sxp + r * sstride + 8 * c)), xs = __uint_as_float(lds32(xsp + r * sstride + 8 * c));
+            yg[r] += ds[c] * (sc * (float)(128 * acc[r][c][0] + acc[r][c][1]) - 32.0f * xs);
+            yg8[r] += ds8[c] * (sc * (float)(128 * acc[r][c][2] + acc[r][c][3]) - 32.0f * xs);
+        }
     }
 }
 
@@ -878,10 +912,13 @@ __device__ __forceinline__ int segment_of(const GemvParams &p, int rt) {
 // Inside a CTA the work is cut into units = (row tile, k part); warp w takes units w, w + nwarps, ...
 // and streams each unit's tiles through its private ring of shared-memory slots.
 // Shared memory: staged x | aux sums | partial sums per unit | tile rings | mbarriers.
-template <int TYPE, int NB, bool I8>
+// MI = 0: fp16 path with NB groups of 8 batch columns; MI = 1, 2: integer path for MI batch rows.
+template <int TYPE, int NB, int MI>
 __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
-    static_assert(!I8 || NB == 1, "the integer path exists at m = 1");
+    constexpr bool I8 = MI > 0;
+    static_assert(!I8 || NB == 1, "the integer path serves m <= 2");
     using IF = I8Fmt<TYPE>;
+    constexpr int MR = I8 ? MI : 1;
     using F = Fmt<TYPE>;
     extern __shared__ __align__(128) uint8_t smem[];
     B200Q_TRACE_POINT(0);
@@ -897,11 +934,12 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
     __half *xs = reinterpret_cast<__half *>(smem);
     __half *shi = nullptr, *slo = nullptr;
     float *sx = nullptr, *xsum = nullptr;  // integer path: s and s * sum(xq) per 32-value sub-block
-    if constexpr (I8) {
-        off += dig_region_bytes<TYPE>(p.kts);
+    const uint32_t dstride = (uint32_t)dig_region_bytes<TYPE>(p.kts), sstride = (uint32_t)(kc / IF::BLK) * 4;
+    if constexpr (I8) {  // per batch row: digit arrays; then s[row][sub-block], then s*sum(xq)[row][sub-block]
+        off += (size_t)MR * dstride;
         sx = reinterpret_cast<float *>(smem + off);
-        xsum = sx + kc / IF::BLK;
-        off += (size_t)(kc / IF::BLK) * 8;
+        xsum = sx + MR * (kc / IF::BLK);
+        off += (size_t)MR * sstride * 2;
     } else {
         off += (size_t)p.m * xs_stride * 2;
         shi = reinterpret_cast<__half *>(smem + off);
@@ -1028,7 +1066,10 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
     }
     if (kt_begin < kt_end) {
         if constexpr (I8) {
-            stage_x_i8<TYPE>(p, (int64_t)kt_begin * F::TK, (kt_end - kt_begin) * F::TK, smem, sx, xsum);
+#pragma unroll
+            for (int r = 0; r < MR; r++)
+                stage_x_i8<TYPE>(p, r, (int64_t)kt_begin * F::TK, (kt_end - kt_begin) * F::TK, smem + (size_t)r * dstride,
+                                 sx + r * (kc / IF::BLK), xsum + r * (kc / IF::BLK));
         } else {
             stage_x<TYPE>(p, (int64_t)kt_begin * F::TK, (kt_end - kt_begin) * F::TK, xs_stride, ns, xs, shi, slo);
         }
@@ -1055,7 +1096,7 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
         // The activation addresses of the unit's first tile; every further tile is a constant step on.
         XCols<NB> xc;
         xcols_for_tile<NB>(xc, xb, (k0 - kt_begin) * 32, F::SUB ? (k0 - kt_begin) * (F::TK / F::SUB) : 0, swz_a, swz_b);
-        float yg = 0.0f, yg8 = 0.0f;  // integer path: rows g and g+8, this lane's K quarter
+        float yg[MR] = {}, yg8[MR] = {};  // integer path: rows g and g+8 per batch row, this lane's K quarter
         constexpr int kDigTile = 256 + IF::PAD, kScaleTile = 256 / IF::BLK * 4;  // bytes per tile: digits, scales
         uint32_t dig = dig_lane + (k0 - kt_begin) * kDigTile, sxp = sx_lane + (k0 - kt_begin) * kScaleTile,
                  xsp = xs_lane + (k0 - kt_begin) * kScaleTile;
@@ -1069,13 +1110,13 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
             for (int ti = 0; ti < nt; ti++) {
                 if constexpr (I8) {
                     if constexpr (TYPE == kQ4_K) {
-                        tile_q4_k_i8(tile, lane, dig, sxp, xsp, yg, yg8);
+                        tile_q4_k_i8<MR>(tile, lane, dig, sxp, xsp, dstride, sstride, yg, yg8);
                     } else if constexpr (TYPE == kQ6_K) {
-                        tile_q6_k_i8(tile, lane, dig, sxp, xsp, yg, yg8);
+                        tile_q6_k_i8<MR>(tile, lane, dig, sxp, xsp, dstride, sstride, yg, yg8);
                     } else if constexpr (TYPE == kQ4_0) {
-                        tile_q4_0_i8(tile, lane, dig, sxp, xsp, yg, yg8);
+                        tile_q4_0_i8<MR>(tile, lane, dig, sxp, xsp, dstride, sstride, yg, yg8);
                     } else {
-                        tile_q8_0_i8(tile, lane, dig, sxp, xsp, yg, yg8);
+                        tile_q8_0_i8<MR>(tile, lane, dig, sxp, xsp, dstride, sstride, yg, yg8);
                     }
                     dig += kDigTile, sxp += kScaleTile, xsp += kScaleTile;
                 } else if constexpr (TYPE == kQ4_0) {
@@ -1104,10 +1145,22 @@ __global__ void __launch_bounds__(512, 1) gemv_mma_kernel(const GemvParams p) {
                 issue_next();
             }
         }
-        if constexpr (I8) {  // add the four K quarters of a row; lane t = 0 holds batch column 0 of rows g, g+8
-            yg += __shfl_xor_sync(0xffffffffu, yg, 1), yg8 += __shfl_xor_sync(0xffffffffu, yg8, 1);
-            yg += __shfl_xor_sync(0xffffffffu, yg, 2), yg8 += __shfl_xor_sync(0xffffffffu, yg8, 2);
-            acc[0][0][0] = t == 0 ? yg : 0.0f, acc[0][0][2] = t == 0 ? yg8 : 0.0f;
+        if constexpr (I8) {
+            // Add the four K quarters of a row, then hand the sums over in the accumulator layout the epilogue
+            // expects: lane (g, t), element i = row g + 8*(i >> 1), batch column 2t + (i & 1).
+#pragma unroll
+            for (int r = 0; r < MR; r++) {
+                yg[r] += __shfl_xor_sync(0xffffffffu, yg[r], 1), yg8[r] += __shfl_xor_sync(0xffffffffu, yg8[r], 1);
+                yg[r] += __shfl_xor_sync(0xffffffffu, yg[r], 2), yg8[r] += __shfl_xor_sync(0xffffffffu, yg8[r], 2);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                float v = 0.0f;
+#pragma unroll
+                for (int r = 0; r < MR; r++)
+                    if (2 * t + (i & 1) == r) v = (i >> 1) ? yg8[r] : yg[r];
+                acc[0][0][i] = v;
+            }
         }
         float *r = red + (size_t)(crow * p.kp + cpart) * NB * 128 + lane;
 #pragma unroll
@@ -1234,8 +1287,9 @@ Plan make_plan(int64_t rt, int64_t kt, int sms, int max_warps, size_t x_bytes_pe
     return best;
 }
 
-template <int TYPE, int NB, bool I8>
+template <int TYPE, int NB, int MI>
 int launch_t(const Weight &w, const GemvParams &p0, cudaStream_t s) {
+    constexpr bool I8 = MI > 0;
     using F = Fmt<TYPE>;
     GemvParams p = p0;
     int dev_sms = 148;
@@ -1275,7 +1329,7 @@ int launch_t(const Weight &w, const GemvParams &p0, cudaStream_t s) {
     p.tps = std::max(1, std::min(p.ktp, env_int("B200Q_GEMV_TPS", F::TILE <= 2304 ? 2 : 1)));
 
     const size_t x_bytes =
-        I8 ? ((dig_region_bytes<TYPE>(p.kts) + (size_t)p.kts * 2 * 4 * (256 / I8Fmt<TYPE>::BLK) + 15) & ~(size_t)15)
+        I8 ? (((size_t)MI * (dig_region_bytes<TYPE>(p.kts) + (size_t)p.kts * 2 * 4 * (256 / I8Fmt<TYPE>::BLK)) + 15) & ~(size_t)15)
            : ((((size_t)p.m * (p.kts * F::TK + 8) * 2 + (F::SUB ? (size_t)p.m * (p.kts * F::TK / F::SUB) * 4 : 0)) + 15) & ~(size_t)15);
     const size_t red_bytes = (size_t)p.maxunits * NB * 128 * sizeof(float);
     const size_t fixed = (x_bytes + red_bytes + 127) & ~(size_t)127;
@@ -1294,7 +1348,7 @@ int launch_t(const Weight &w, const GemvParams &p0, cudaStream_t s) {
     p.pre_issue = std::max(1, std::min(depth, env_int("B200Q_GEMV_PRE", depth)));
     const size_t smem = fixed + (size_t)warps * depth * slot_bytes + (size_t)warps * depth * 8;
 
-    auto kern = gemv_mma_kernel<TYPE, NB, I8>;
+    auto kern = gemv_mma_kernel<TYPE, NB, MI>;
     static thread_local bool configured[16] = {};
     if (!configured[w.device & 15]) {
         B200Q_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit));
@@ -1320,16 +1374,14 @@ int launch_t(const Weight &w, const GemvParams &p0, cudaStream_t s) {
 
 template <int TYPE>
 int launch_nb(const Weight &w, const GemvParams &p, cudaStream_t s) {
-    {
-        // m = 1: integer tensor-core path (B200Q_GEMV_I8=0 selects the fp16 path, for comparisons)
-        // Measured faster than the fp16 path from the smallest decoder matrices (1024 x 4096) up, so the size
-        // threshold defaults to none.
-        // (read at every launch so that tests can force either path: 0 = never, 1 = by size, 2 = always)
-        const int i8 = env_int("B200Q_GEMV_I8", 1);
-        const int i8_min_tiles = env_int("B200Q_GEMV_I8_MIN_TILES", 0);
-        if (i8 != 0 && p.m == 1 && (i8 == 2 || w.rt * w.kt >= (int64_t)i8_min_tiles * 148)) return launch_t<TYPE, 1, true>(w, p, s);
+    // m <= 2: integer tensor-core path, faster than the fp16 path from the smallest decoder matrices
+    // (1024 x 4096) up; from m = 4 its one MMA set per batch row costs more than it saves (measured 17.7 against
+    // 13.5 us on 14336 x 4096).  B200Q_GEMV_I8=0 (read at every launch) selects the fp16 path for comparisons.
+    if (env_int("B200Q_GEMV_I8", 1) != 0) {
+        if (p.m == 1) return launch_t<TYPE, 1, 1>(w, p, s);
+        if (p.m == 2) return launch_t<TYPE, 1, 2>(w, p, s);
     }
-    return p.m <= 8 ? launch_t<TYPE, 1, false>(w, p, s) : launch_t<TYPE, 2, false>(w, p, s);
+    return p.m <= 8 ? launch_t<TYPE, 1, 0>(w, p, s) : launch_t<TYPE, 2, 0>(w, p, s);
 }
 
 }  // namespace

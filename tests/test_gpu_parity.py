@@ -305,8 +305,8 @@ def test_mixed_format_batch_side_by_side(oracle, m):
 # ----------------------------------------------------------------------------- integer decode path
 @pytest.fixture
 def force_integer_path(monkeypatch):
-    """The m = 1 integer tensor-core path is chosen by matrix size; tests force it on small matrices."""
-    monkeypatch.setenv("B200Q_GEMV_I8", "2")
+    """The integer tensor-core path is the default for m <= 2; the variable only guards against an outer override."""
+    monkeypatch.setenv("B200Q_GEMV_I8", "1")
 
 
 @pytest.mark.parametrize("name", ["Q4_K", "Q6_K", "Q4_0", "Q8_0"])
@@ -327,6 +327,23 @@ def test_integer_path_parity(oracle, force_integer_path, name, n, k):
     refb = oracle.dense(int(t), w, torch.from_numpy(x).to(torch.bfloat16).float().numpy(), bias, 0, route="f64")
     assert rel_err(yb.cpu().numpy(), refb) <= 2e-4
     wr.free()
+
+
+@pytest.mark.parametrize("name", ["Q4_K", "Q6_K", "Q4_0", "Q8_0"])
+@pytest.mark.parametrize("m", [2])
+def test_integer_path_small_batches(oracle, name, m):
+    """m = 2: the codes are unpacked once and multiplied with both batch rows' digits."""
+    t = TYPES[name]
+    n, k = 200, 2048
+    w = oracle.make_weights(int(t), n, k, seed=m)
+    rng = np.random.default_rng(50 + m)
+    x = rng.standard_normal((m, k)).astype(np.float32) * np.array([1.0, 30.0, 0.01, 5.0])[:m, None].astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    ref = oracle.dense(int(t), w, x, bias, 0, route="f64")
+    y = g.quantized_dense(torch.from_numpy(x).cuda(), w, quant(t), torch.from_numpy(bias).cuda())
+    assert g.last_kernel() == nat.KERNEL_GEMV_MMA
+    err = np.abs(y.cpu().numpy() - ref).max(axis=1) / np.abs(ref).max(axis=1)   # per batch row: their scales differ
+    assert err.max() <= 2e-4, err
 
 
 @pytest.mark.parametrize("name", ["Q4_0", "Q8_0"])
