@@ -249,7 +249,7 @@ def run_cuda(args) -> None:
                         last = name
                     pending = sig
                     if args.order == "barrier" and last in sync_after:
-                        bufs.barrier()
+                        bufs.barrier(native=args.barrier == "native")
                 elif gather == "nccl":
                     g.backend_fused_quantized_dense(x_dev[k], weights[li][pi], None, quant[t], acts[act], out=y_loc[li][pi])
                     dist.all_gather_into_tensor(y_full[li][pi], y_loc[li][pi])
@@ -270,7 +270,7 @@ def run_cuda(args) -> None:
 
         def step():  # close the step: the last signal is consumed by a device barrier, not by a next launch
             _inner()
-            bufs.barrier()
+            bufs.barrier(native=args.barrier == "native")
 
     def select(pred):
         def run():
@@ -367,7 +367,7 @@ def run_cuda(args) -> None:
         "config": {"workload": WORKLOAD, "batch": batch, "weight_bytes_per_step": total_bytes,
                    "parallelism": f"rows/{world}" + {"none": "", "nccl": " + NCCL all-gather per projection",
                                                            "peer": " + all-gather fused into the GEMV epilogue (NVLink peer stores), " +
-                                                                   ("4 device barriers per layer" if args.order == "barrier" else "ranks ordered inside the kernels at 4 points per layer")}[gather],
+                                                                   ("4 device barriers per layer (" + args.barrier + ")" if args.order == "barrier" else "ranks ordered inside the kernels at 4 points per layer")}[gather],
                    "inputs": "fixed N(0,1) activations per projection (outputs not chained)",
                    "l2": f"no flush: {local_bytes / 1e6:.0f} MB of weights per GPU per step exceed the 126 MB L2",
                    "launch": (("one CUDA graph per step; q+k and gate+up of a layer share one launch each (160 launches)" +
@@ -417,6 +417,8 @@ def main() -> None:
                     help="N > 1 with --gather peer: order the ranks with device barriers between launches (default) "
                          "or with completion counters inside the GEMV kernels (experimental)")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"], help="N > 1: how outputs are all-gathered")
+    ap.add_argument("--barrier", default="torch", choices=["native", "torch"],
+                    help="N > 1 with --gather peer: the library's one-CTA barrier kernel or torch's symmetric-memory barrier")
     ap.add_argument("--traffic", type=float, default=None, help="dram bytes per launch of the dominant kernel (ncu)")
     args = ap.parse_args()
     if args.impl == "reference":

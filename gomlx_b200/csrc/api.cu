@@ -421,6 +421,13 @@ int b200q_dense_scatter(b200q_weight_t h, const void *x_dev, int x_dtype, int64_
                                      sync_local, sync_peers, rank, sync_flags, stream);
 }
 
+int b200q_peer_barrier(int device, int *sync_local, int *const *sync_peers, int n_peers, int rank, void *stream) {
+    if (!sync_local || n_peers < 0 || n_peers > 7 || (n_peers > 0 && !sync_peers) || rank < 0 || rank > n_peers)
+        return fail(B200Q_EINVAL, "peer_barrier: needs the sync words of every rank and a valid rank");
+    B200Q_CUDA(cudaSetDevice(device));
+    return launch_peer_barrier(sync_local, sync_peers, n_peers, rank, sync_local + 25, static_cast<cudaStream_t>(stream));
+}
+
 int b200q_dense_f32_prefill_noalloc(b200q_weight_t h, const float *x_dev, int64_t m, const float *bias_dev,
                                     int activation, float *y_dev, int64_t y_ld, void *stream) {
     auto w = find(h);

@@ -50,6 +50,9 @@ int launch_gemv_batch(int count, const Weight *const *ws, const void *x, int x_d
                       const int64_t *y_peer_deltas = nullptr, int npeers = 0, int *sync_local = nullptr,
                       int *const *sync_peers = nullptr, int rank = 0, int sync_flags = 0, int sm_limit = 0);
 
+// peer.cu: rendezvous of the GPUs of a row-sharded layer (one thread per peer, bounded waits)
+int launch_peer_barrier(int *sync_local, int *const *sync_peers, int npeers, int rank, int *status, cudaStream_t s);
+
 // gemm_tcgen05.cu
 int launch_gemm(const Weight &w, const void *x, int x_dtype, int64_t m, const float *bias, int act, float *y,
                 int64_t y_ld, cudaStream_t s);

@@ -1,0 +1,72 @@
+// Device-side barrier between the GPUs of a row-sharded layer, as one tiny kernel.
+//
+// A row-sharded decoder layer consumes the gathered outputs of its projections (the reference shards
+// with its SPMD mesh, core/graph/distributed.go:117-141, and leaves the collective to the backend), so
+// the ranks have to meet where those outputs are read: after q/k/v, o, gate/up and down.  The fused
+// scatter epilogue of the GEMV already put every value into every GPU's buffer; what is left of the
+// all-gather is this rendezvous.  It is a kernel of its own (one CTA, one thread per peer) so that it can
+// sit between two GEMV launches of a CUDA graph and take part in programmatic dependent launch: it lets
+// the next GEMV start its prologue (barrier set-up, weight prefetch) while the ranks are still meeting.
+//
+// Sync words (int32, in every rank's peer-mapped buffer): word 16 + r = number of barriers rank r has
+// entered (written by rank r into every rank's copy), word 24 = this rank's own count.  Every wait is
+// bounded; a peer that never arrives is reported through the status word, the kernel returns.
+#include "common.cuh"
+
+namespace b200q {
+namespace {
+
+constexpr int kBarrierSlot = 16, kBarrierCount = 24;
+constexpr int kBarrierSpinLimit = 1 << 22;
+
+struct PeerWords {
+    int *peer[7];
+};
+
+__global__ void __launch_bounds__(32, 1) peer_barrier_kernel(int *local, PeerWords peers, int npeers, int rank, int *status) {
+    // the next kernel in the stream may begin its prologue; it waits for this grid before touching activations
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // everything the previous kernel of this stream wrote (also into peer memory) is performed
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ int epoch;
+    if (threadIdx.x == 0) {
+        epoch = local[kBarrierCount] + 1;
+        local[kBarrierCount] = epoch;
+    }
+    __syncthreads();
+    const int e = epoch;
+    if ((int)threadIdx.x < npeers) {
+        const int pr = (int)threadIdx.x < rank ? (int)threadIdx.x : (int)threadIdx.x + 1;  // rank of peer number threadIdx.x
+        __threadfence_system();
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(peers.peer[threadIdx.x] + kBarrierSlot + rank), "r"(e) : "memory");
+        bool arrived = false;
+        for (int spin = 0; spin < kBarrierSpinLimit && !arrived; spin++) {
+            int v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(local + kBarrierSlot + pr) : "memory");
+            arrived = v - e >= 0;
+        }
+        if (!arrived && status != nullptr) atomicExch(status, 2);
+        __threadfence_system();
+    }
+}
+
+}  // namespace
+
+int launch_peer_barrier(int *sync_local, int *const *sync_peers, int npeers, int rank, int *status, cudaStream_t s) {
+    PeerWords pw{};
+    for (int i = 0; i < npeers; i++) pw.peer[i] = sync_peers[i];
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, 1, 1);
+    cfg.blockDim = dim3(32, 1, 1);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200Q_CUDA(cudaLaunchKernelEx(&cfg, peer_barrier_kernel, sync_local, pw, npeers, rank, status));
+    return 0;
+}
+
+}  // namespace b200q

@@ -99,6 +99,7 @@ class PeerScatterBuffers:
         self.handle = symm_mem.rendezvous(self._all, group.group_name)
         self._ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self._all.zero_()
+        self._sync_peers = None
         self.local = self._all[self.SYNC_WORDS:]
         torch.cuda.synchronize()
         self.handle.barrier(channel=0)  # every rank's sync words are zero before anyone signals
@@ -110,8 +111,25 @@ class PeerScatterBuffers:
     def sync_ptr(self, rank: int) -> int:
         return self._ptrs[rank]
 
-    def barrier(self) -> None:
-        self.handle.barrier(channel=0)
+    def barrier(self, native: bool = False) -> None:
+        """Device-side rendezvous of all ranks on the current stream.  ``native``: the library's one-CTA barrier
+        kernel (``b200q_peer_barrier``, overlaps the next launch's prologue); otherwise the symmetric-memory
+        barrier of torch."""
+        if not native:
+            self.handle.barrier(channel=0)
+            return
+        import ctypes
+        from . import _native as nat
+        if self._sync_peers is None:
+            peers = [self.sync_ptr(r) for r in range(self.world) if r != self.rank]
+            self._sync_peers = (ctypes.c_void_p * max(1, len(peers)))(*peers)
+        nat.check(nat.lib().b200q_peer_barrier(self._all.device.index, ctypes.c_void_p(self.sync_ptr(self.rank)), self._sync_peers,
+                                               self.world - 1, self.rank, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
+    def barrier_timed_out(self) -> bool:
+        """True if a native barrier gave up waiting for a peer (synchronizes the device)."""
+        torch.cuda.synchronize()
+        return int(self._all[:self.SYNC_WORDS].view(torch.int32)[25].item()) == 2
 
 
 class PeerScatterDense:

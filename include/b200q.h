@@ -169,6 +169,16 @@ int b200q_dense_batch_scatter(int count, const b200q_weight_t *shards, const voi
                               float *const *y_peers, int n_peers, const int64_t *y_lds, const int64_t *row_offsets,
                               int *sync_local, int *const *sync_peers, int rank, int sync_flags, void *stream);
 
+/* Rendezvous of the ranks of a row-sharded layer, enqueued on `stream`: returns on the device once every rank
+ * has entered its barrier with the same ordinal; everything a rank stored before it (b200q_dense_scatter writes
+ * into peer buffers) is visible to all ranks after it.  It is the remainder of the all-gather the reference's
+ * SPMD partitioning (core/graph/distributed.go:117-141) would place after a sharded projection.  sync_local /
+ * sync_peers / rank as for b200q_dense_scatter (this call uses words 16..25 of the 64 sync words; word 25 becomes
+ * 2 if a peer did not arrive within the bounded wait).  One small kernel; it takes part in programmatic dependent
+ * launch, so the next b200q_dense* call on the stream overlaps its prologue with the rendezvous.  All ranks must
+ * call it the same number of times. */
+int b200q_peer_barrier(int device, int *sync_local, int *const *sync_peers, int n_peers, int rank, void *stream);
+
 /* No counterpart in the reference: an allocation-free form of b200q_dense for prefill (m > 16) with f32
  * activations.  b200q_dense converts f32 activations to bf16 in a buffer it takes from the CUDA
  * stream-ordered allocator; callers that must not allocate at that point (a serving loop inside an
