@@ -234,16 +234,17 @@ def run_cuda(args) -> None:
         pending = False  # a signal has been published that the next launch has to wait for
         for li in range(LAYERS):
             for pi, (name, t, _, k, act) in enumerate(PROJECTIONS):
-                if gather == "peer" and args.fuse_shared_input and name in ("k", "up"):
+                qkv = args.fuse_shared_input >= 2 and args.order == "barrier"  # v beside q+k (no sync words on mixed calls)
+                if gather == "peer" and args.fuse_shared_input and (name in ("k", "up") or (name == "v" and qkv)):
                     continue  # computed together with q / gate
                 if gather == "peer":
                     sig = args.order == "kernel" and name in sync_after
-                    if args.fuse_shared_input and name in ("q", "gate"):  # q+k, gate+up: one launch each
-                        peer_scatter_batch([peer_layers[li][pi], peer_layers[li][pi + 1]], x_dev[k], None,
-                                           [act_types[act], act_types[PROJECTIONS[pi + 1][4]]],
-                                           wait=pending, signal=sig or (args.order == "kernel" and PROJECTIONS[pi + 1][0] in sync_after))
-                        sig = sig or (args.order == "kernel" and PROJECTIONS[pi + 1][0] in sync_after)
-                        last = PROJECTIONS[pi + 1][0]
+                    if args.fuse_shared_input and name in ("q", "gate"):  # q+k(+v), gate+up: one call each
+                        group = [pi, pi + 1] + ([pi + 2] if (name == "q" and qkv) else [])
+                        sig = sig or (args.order == "kernel" and any(PROJECTIONS[pj][0] in sync_after for pj in group))
+                        peer_scatter_batch([peer_layers[li][pj] for pj in group], x_dev[k], None,
+                                           [act_types[PROJECTIONS[pj][4]] for pj in group], wait=pending, signal=sig)
+                        last = PROJECTIONS[group[-1]][0]
                     else:
                         peer_layers[li][pi](x_dev[k], None, act_types[act], wait=pending, signal=sig)
                         last = name
@@ -371,7 +372,7 @@ def run_cuda(args) -> None:
                    "inputs": "fixed N(0,1) activations per projection (outputs not chained)",
                    "l2": f"no flush: {local_bytes / 1e6:.0f} MB of weights per GPU per step exceed the 126 MB L2",
                    "launch": (("one CUDA graph per step; q+k and gate+up of a layer share one launch each (160 launches)" +
-                               ("; v runs next to q+k on its share of the SMs" if (args.fuse_shared_input >= 2 and gather == "none") else ""))
+                               ("; v runs next to q+k on its share of the SMs" if (args.fuse_shared_input >= 2 and (gather == "none" or (gather == "peer" and args.order == "barrier"))) else ""))
                               if (args.fuse_shared_input and gather in ("none", "peer")) else "one CUDA graph of 224 GEMV launches per step")},
         "roofline": roofline,
         "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": ms_e2e,

@@ -82,36 +82,31 @@ int side_streams(int device, SideStreams **out) {
     return 0;
 }
 
-// b200q_dense_batch for matrices that cannot share one launch.  Decode shapes on one device are grouped by
-// (format, K); every group is one launch, the groups run side by side on forked streams with the SMs divided
-// in proportion to their bytes (small decode launches are bound by latency, not by SM count), and the caller's
-// stream waits for all of them.  Everything else falls back to one b200q_dense call per matrix.
-int dense_batch_mixed(int count, const b200q_weight_t *hs, const std::vector<std::shared_ptr<Weight>> &ws, const void *x_dev,
-                      int x_dtype, int64_t m, const float *const *biases_dev, const int *activations, float *const *ys_dev,
-                      const int64_t *y_lds, void *stream) {
-    bool one_device = true;
-    for (int i = 1; i < count; i++) one_device = one_device && ws[i]->device == ws[0]->device;
+// Groups decode matrices on one device by (format, K), at most four per group.  Empty result: not groupable
+// (more than four groups).
+std::vector<std::vector<int>> format_groups(const std::vector<std::shared_ptr<Weight>> &ws, int count) {
     std::vector<std::vector<int>> groups;
-    if (m <= 16 && one_device) {
-        for (int i = 0; i < count; i++) {
-            bool placed = false;
-            for (auto &g : groups) {
-                if (g.size() < 4 && ws[g[0]]->type == ws[i]->type && ws[g[0]]->k == ws[i]->k) {
-                    g.push_back(i), placed = true;
-                    break;
-                }
+    for (int i = 0; i < count; i++) {
+        bool placed = false;
+        for (auto &g : groups) {
+            if (g.size() < 4 && ws[g[0]]->type == ws[i]->type && ws[g[0]]->k == ws[i]->k) {
+                g.push_back(i), placed = true;
+                break;
             }
-            if (!placed) groups.push_back({i});
         }
+        if (!placed) groups.push_back({i});
     }
-    if (groups.empty() || groups.size() > 4) {
-        for (int i = 0; i < count; i++) {
-            int rc = b200q_dense(hs[i], x_dev, x_dtype, m, biases_dev ? biases_dev[i] : nullptr, activations[i], ys_dev[i],
-                                 y_lds ? y_lds[i] : 0, stream);
-            if (rc != 0) return rc;
-        }
-        return B200Q_OK;
-    }
+    if (groups.size() > 4) groups.clear();
+    return groups;
+}
+
+// One launch per group, the groups side by side on streams forked from `stream` with the SMs divided in
+// proportion to their bytes (small decode launches are bound by latency, not by SM count); `stream` waits for
+// all of them.  ys: output pointers (already at the shard's first column for scatter calls); peer_deltas /
+// n_peers as for launch_gemv_batch.
+int launch_format_groups(const std::vector<std::vector<int>> &groups, const std::vector<std::shared_ptr<Weight>> &ws,
+                         const void *x_dev, int x_dtype, int64_t m, const float *const *biases_dev, const int *activations,
+                         float *const *ys, const int64_t *lds_in, void *stream, const int64_t *peer_deltas, int n_peers) {
     const int device = ws[0]->device;
     B200Q_CUDA(cudaSetDevice(device));
     int sms = 148;
@@ -147,17 +142,38 @@ int dense_batch_mixed(int count, const b200q_weight_t *hs, const std::vector<std
         int acts[4];
         int n = 0;
         for (int i : groups[g]) {
-            wp[n] = ws[i].get(), bp[n] = biases_dev ? biases_dev[i] : nullptr, yp[n] = ys_dev[i], acts[n] = activations[i];
-            lds[n] = (y_lds && y_lds[i]) ? y_lds[i] : ws[i]->n;
+            wp[n] = ws[i].get(), bp[n] = biases_dev ? biases_dev[i] : nullptr, yp[n] = ys[i], acts[n] = activations[i];
+            lds[n] = (lds_in && lds_in[i]) ? lds_in[i] : ws[i]->n;
             n++;
         }
-        int rc = launch_gemv_batch(n, wp, x_dev, x_dtype, (int)m, bp, acts, yp, lds, gs, nullptr, 0, nullptr, nullptr, 0, 0, share);
+        int rc = launch_gemv_batch(n, wp, x_dev, x_dtype, (int)m, bp, acts, yp, lds, gs, peer_deltas, n_peers, nullptr, nullptr, 0, 0,
+                                   share);
         if (rc != 0) return rc;
         if (g > 0) B200Q_CUDA(cudaEventRecord(ss->join[g - 1], gs));
     }
     for (size_t g = 1; g < groups.size(); g++) B200Q_CUDA(cudaStreamWaitEvent(s, ss->join[g - 1], 0));
     g_last_kernel = B200Q_KERNEL_GEMV_MMA;
     return B200Q_OK;
+}
+
+// b200q_dense_batch for matrices that cannot share one launch: decode shapes on one device run as format groups
+// side by side, everything else falls back to one b200q_dense call per matrix.
+int dense_batch_mixed(int count, const b200q_weight_t *hs, const std::vector<std::shared_ptr<Weight>> &ws, const void *x_dev,
+                      int x_dtype, int64_t m, const float *const *biases_dev, const int *activations, float *const *ys_dev,
+                      const int64_t *y_lds, void *stream) {
+    bool one_device = true;
+    for (int i = 1; i < count; i++) one_device = one_device && ws[i]->device == ws[0]->device;
+    std::vector<std::vector<int>> groups;
+    if (m <= 16 && one_device) groups = format_groups(ws, count);
+    if (groups.empty()) {
+        for (int i = 0; i < count; i++) {
+            int rc = b200q_dense(hs[i], x_dev, x_dtype, m, biases_dev ? biases_dev[i] : nullptr, activations[i], ys_dev[i],
+                                 y_lds ? y_lds[i] : 0, stream);
+            if (rc != 0) return rc;
+        }
+        return B200Q_OK;
+    }
+    return launch_format_groups(groups, ws, x_dev, x_dtype, m, biases_dev, activations, ys_dev, y_lds, stream, nullptr, 0);
 }
 
 }  // namespace
@@ -370,8 +386,8 @@ int b200q_dense_batch_scatter(int count, const b200q_weight_t *hs, const void *x
                               const float *const *biases_dev, const int *activations, float *const *y_locals,
                               float *const *y_peers, int n_peers, const int64_t *y_lds, const int64_t *row_offsets,
                               int *sync_local, int *const *sync_peers, int rank, int sync_flags, void *stream) {
-    if (count < 1 || count > 4 || !hs || !y_locals || !activations || !y_lds || !row_offsets)
-        return fail(B200Q_EINVAL, "dense_batch_scatter: 1..4 matrices with outputs, leading dimensions and row offsets");
+    if (count < 1 || count > 16 || !hs || !y_locals || !activations || !y_lds || !row_offsets)
+        return fail(B200Q_EINVAL, "dense_batch_scatter: 1..16 matrices with outputs, leading dimensions and row offsets");
     if (m == 0) return B200Q_OK;
     if (m < 0 || m > 16) return fail(B200Q_ENOTIMPL, "dense_batch_scatter: only the decode path (m <= 16) scatters to peers");
     if (!x_dev) return fail(B200Q_EINVAL, "dense_batch_scatter: null x");
@@ -381,33 +397,42 @@ int b200q_dense_batch_scatter(int count, const b200q_weight_t *hs, const void *x
         return fail(B200Q_EINVAL, "dense_batch_scatter: sync flags need the sync words of every rank and a valid rank");
     if (reinterpret_cast<uintptr_t>(x_dev) & 15) return fail(B200Q_EINVAL, "dense_batch_scatter: x must be 16-byte aligned");
     std::vector<std::shared_ptr<Weight>> ws((size_t)count);
-    const Weight *wp[4];
-    float *ys[4];
+    std::vector<float *> ys((size_t)count);
     int64_t deltas[7] = {};
+    bool same = count <= 4;
     for (int i = 0; i < count; i++) {
         ws[i] = find(hs[i]);
         if (!ws[i]) return fail(B200Q_EHANDLE, "dense_batch_scatter: unknown handle");
-        wp[i] = ws[i].get();
         if (!y_locals[i]) return fail(B200Q_EINVAL, "dense_batch_scatter: null y");
         if (activations[i] < B200Q_ACT_NONE || activations[i] > B200Q_ACT_TANH) return fail(B200Q_EINVAL, "dense_batch_scatter: bad activation");
         if (row_offsets[i] < 0 || y_lds[i] < row_offsets[i] + ws[i]->n)
             return fail(B200Q_EINVAL, "dense_batch_scatter: y_ld smaller than row_offset + N");
-        if (ws[i]->type != ws[0]->type || ws[i]->k != ws[0]->k || ws[i]->device != ws[0]->device)
-            return fail(B200Q_EINVAL, "dense_batch_scatter: matrices of one launch must share format, K and device");
+        if (ws[i]->device != ws[0]->device) return fail(B200Q_EINVAL, "dense_batch_scatter: matrices of one call must be on one device");
+        same = same && ws[i]->type == ws[0]->type && ws[i]->k == ws[0]->k;
         ys[i] = y_locals[i] + row_offsets[i];
-        // every output of the launch must sit at the same distance from its copy on a given peer
+        // every output of the call must sit at the same distance from its copy on a given peer
         for (int r = 0; r < n_peers; r++) {
             float *peer = y_peers[(size_t)i * n_peers + r];
             if (!peer) return fail(B200Q_EINVAL, "dense_batch_scatter: null peer pointer");
             const int64_t d = reinterpret_cast<intptr_t>(peer) - reinterpret_cast<intptr_t>(y_locals[i]);
             if (i == 0) deltas[r] = d;
             else if (deltas[r] != d)
-                return fail(B200Q_EINVAL, "dense_batch_scatter: the outputs of one launch must lie in one peer-mapped buffer per GPU");
+                return fail(B200Q_EINVAL, "dense_batch_scatter: the outputs of one call must lie in one peer-mapped buffer per GPU");
         }
     }
     B200Q_CUDA(cudaSetDevice(ws[0]->device));
     g_last_kernel = B200Q_KERNEL_GEMV_MMA;
-    return launch_gemv_batch(count, wp, x_dev, x_dtype, (int)m, biases_dev, activations, ys, y_lds, static_cast<cudaStream_t>(stream),
+    if (!same) {
+        // different formats (q and k next to v): one launch per format group, side by side; ordering by sync
+        // words belongs to single launches
+        if (sync_flags != 0) return fail(B200Q_EINVAL, "dense_batch_scatter: sync flags need matrices of one format and K");
+        std::vector<std::vector<int>> groups = format_groups(ws, count);
+        if (groups.empty()) return fail(B200Q_EINVAL, "dense_batch_scatter: too many different formats in one call");
+        return launch_format_groups(groups, ws, x_dev, x_dtype, m, biases_dev, activations, ys.data(), y_lds, stream, deltas, n_peers);
+    }
+    const Weight *wp[4];
+    for (int i = 0; i < count; i++) wp[i] = ws[i].get();
+    return launch_gemv_batch(count, wp, x_dev, x_dtype, (int)m, biases_dev, activations, ys.data(), y_lds, static_cast<cudaStream_t>(stream),
                              deltas, n_peers, sync_local, sync_peers, rank, sync_flags);
 }
 

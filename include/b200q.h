@@ -162,8 +162,10 @@ int b200q_dense_scatter(b200q_weight_t w, const void *x_dev, int x_dtype, int64_
  * the caller in ml/zoo/transformer/transformer.go:1049-1054,1286-1294 applies them to one x): one launch.
  * Arrays have `count` entries; y_peers is [count][n_peers] flattened (matrix i, peer r at i*n_peers + r) and
  * every matrix' outputs must lie in the same peer-mapped buffer per GPU, i.e. y_peers[i][r] - y_locals[i] must
- * not depend on i (true for regions of one symmetric allocation); otherwise B200Q_EINVAL.  The matrices must
- * share format, K and device.  Sync words and flags as for b200q_dense_scatter. */
+ * not depend on i (true for regions of one symmetric allocation); otherwise B200Q_EINVAL.  Up to four matrices of
+ * one format and K are one launch; with different formats (q and k next to v) the call runs one launch per format
+ * group side by side, as b200q_dense_batch does, and sync_flags must be 0.  Sync words and flags otherwise as for
+ * b200q_dense_scatter. */
 int b200q_dense_batch_scatter(int count, const b200q_weight_t *shards, const void *x_dev, int x_dtype, int64_t m,
                               const float *const *biases_dev, const int *activations, float *const *y_locals,
                               float *const *y_peers, int n_peers, const int64_t *y_lds, const int64_t *row_offsets,

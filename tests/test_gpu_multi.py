@@ -72,6 +72,23 @@ def _worker(rank, world, port, q):
                 bad.append((rank, "batch", float(err)))
         bufs.barrier()
         torch.cuda.synchronize()
+        # mixed formats in one call (q+k in Q4_K beside v in Q6_K): format groups side by side, then the native barrier
+        stage("batched launch")
+        w3 = o.make_weights(o.Q6_K, n2, k, seed=4)
+        lc = PeerScatterDense(w3, g.Quantization(g.QuantizationScheme.GGML, g.GGMLQuantType.Q6_K), bufs, max_m * n, max_m, rank)
+        x = rng.standard_normal((1, k)).astype(np.float32)
+        ya, yc = peer_scatter_batch([layer, lc], torch.from_numpy(x).cuda(), None, [g.Activation.NONE, g.Activation.NONE])
+        bufs.barrier(native=True)
+        torch.cuda.synchronize()
+        for y, ww, tt in ((ya, w, o.Q4_K), (yc, w3, o.Q6_K)):
+            ref = o.dense(tt, ww, x, route="f64")
+            err = np.abs(y.cpu().numpy() - ref).max() / np.abs(ref).max()
+            if not err <= 3e-3:
+                bad.append((rank, "mixed", float(err)))
+        if bufs.barrier_timed_out():
+            bad.append((rank, "native barrier timed out"))
+        bufs.barrier(native=True)
+        torch.cuda.synchronize()
         q.put((rank, "ok" if not bad else repr(bad)))
     except Exception as e:
         q.put((rank, repr(e)))
