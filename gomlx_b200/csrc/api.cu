@@ -25,6 +25,26 @@ int cuda_fail(cudaError_t e, const char *what) {
 
 namespace {
 
+// Makes `device` current for the rest of the calling function and restores the caller's device on return: a
+// host runtime that tracks the current device itself (torch does, through cudaGetDevice) must not find it changed.
+struct DeviceScope {
+    int prev = -1;
+    cudaError_t err = cudaSuccess;
+    explicit DeviceScope(int device) {
+        err = cudaGetDevice(&prev);
+        if (err == cudaSuccess && prev != device) err = cudaSetDevice(device);
+        else if (err == cudaSuccess) prev = -1;  // nothing to restore
+    }
+    ~DeviceScope() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+    DeviceScope(const DeviceScope &) = delete;
+    DeviceScope &operator=(const DeviceScope &) = delete;
+};
+#define B200Q_DEVICE(dev)                                                         \
+    DeviceScope device_scope__(dev);                                              \
+    if (device_scope__.err != cudaSuccess) return cuda_fail(device_scope__.err, "cudaSetDevice")
+
 std::mutex g_mu;
 std::unordered_map<uint64_t, std::shared_ptr<Weight>> g_weights;
 std::atomic<uint64_t> g_next{1};
@@ -108,7 +128,7 @@ int launch_format_groups(const std::vector<std::vector<int>> &groups, const std:
                          const void *x_dev, int x_dtype, int64_t m, const float *const *biases_dev, const int *activations,
                          float *const *ys, const int64_t *lds_in, void *stream, const int64_t *peer_deltas, int n_peers) {
     const int device = ws[0]->device;
-    B200Q_CUDA(cudaSetDevice(device));
+    B200Q_DEVICE(device);
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     double total = 0;
@@ -232,7 +252,7 @@ int b200q_weight_upload(int device, int ggml_type, int64_t n_rows, int64_t k, co
     if (nbytes != n_rows * (k / vpb) * bpb) return fail(B200Q_EINVAL, "weight_upload: nbytes does not match [N, K]");
     if (!bytes) return fail(B200Q_EINVAL, "weight_upload: null data");
     if (n_rows > (int64_t)1 << 31 || k > (int64_t)1 << 30) return fail(B200Q_EINVAL, "weight_upload: weight too large");
-    B200Q_CUDA(cudaSetDevice(device));
+    B200Q_DEVICE(device);
 
     auto w = std::make_shared<Weight>();
     w->type = ggml_type, w->device = device, w->n = n_rows, w->k = k;
@@ -282,7 +302,7 @@ int b200q_weight_free(b200q_weight_t h) {
         w = it->second;
         g_weights.erase(it);
     }
-    B200Q_CUDA(cudaSetDevice(w->device));
+    B200Q_DEVICE(w->device);
     B200Q_CUDA(cudaFree(w->tiles));
     B200Q_CUDA(cudaFree(w->status));
     return B200Q_OK;
@@ -303,7 +323,7 @@ int b200q_weight_info(b200q_weight_t h, int *ggml_type, int64_t *n_rows, int64_t
 int b200q_weight_check(b200q_weight_t h, void *stream) {
     auto w = find(h);
     if (!w) return fail(B200Q_EHANDLE, "weight_check: unknown handle");
-    B200Q_CUDA(cudaSetDevice(w->device));
+    B200Q_DEVICE(w->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     int st = 0;
     B200Q_CUDA(cudaMemcpyAsync(&st, w->status, sizeof(int), cudaMemcpyDeviceToHost, s));
@@ -323,7 +343,7 @@ int b200q_dequantize(b200q_weight_t h, float *out_dev, void *stream) {
     auto w = find(h);
     if (!w) return fail(B200Q_EHANDLE, "dequantize: unknown handle");
     if (!out_dev) return fail(B200Q_EINVAL, "dequantize: null output");
-    B200Q_CUDA(cudaSetDevice(w->device));
+    B200Q_DEVICE(w->device);
     return launch_dequantize(*w, out_dev, static_cast<cudaStream_t>(stream));
 }
 
@@ -340,7 +360,7 @@ int b200q_dense(b200q_weight_t h, const void *x_dev, int x_dtype, int64_t m, con
     if (y_ld < w->n) return fail(B200Q_EINVAL, "dense: y_ld smaller than N");
     if (reinterpret_cast<uintptr_t>(x_dev) & 15) return fail(B200Q_EINVAL, "dense: x must be 16-byte aligned");
     if (m == 0) return B200Q_OK;
-    B200Q_CUDA(cudaSetDevice(w->device));
+    B200Q_DEVICE(w->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (m <= 16) {
         g_last_kernel = B200Q_KERNEL_GEMV_MMA;
@@ -373,7 +393,7 @@ int b200q_dense_batch(int count, const b200q_weight_t *hs, const void *x_dev, in
         int rc = dense_batch_mixed(count, hs, ws, x_dev, x_dtype, m, biases_dev, activations, ys_dev, y_lds, stream);
         return rc;
     }
-    B200Q_CUDA(cudaSetDevice(ws[0]->device));
+    B200Q_DEVICE(ws[0]->device);
     const Weight *wp[4];
     int64_t lds[4];
     for (int i = 0; i < count; i++) wp[i] = ws[i].get(), lds[i] = (y_lds && y_lds[i]) ? y_lds[i] : ws[i]->n;
@@ -420,7 +440,7 @@ int b200q_dense_batch_scatter(int count, const b200q_weight_t *hs, const void *x
                 return fail(B200Q_EINVAL, "dense_batch_scatter: the outputs of one call must lie in one peer-mapped buffer per GPU");
         }
     }
-    B200Q_CUDA(cudaSetDevice(ws[0]->device));
+    B200Q_DEVICE(ws[0]->device);
     g_last_kernel = B200Q_KERNEL_GEMV_MMA;
     if (!same) {
         // different formats (q and k next to v): one launch per format group, side by side; ordering by sync
@@ -449,7 +469,7 @@ int b200q_dense_scatter(b200q_weight_t h, const void *x_dev, int x_dtype, int64_
 int b200q_peer_barrier(int device, int *sync_local, int *const *sync_peers, int n_peers, int rank, void *stream) {
     if (!sync_local || n_peers < 0 || n_peers > 7 || (n_peers > 0 && !sync_peers) || rank < 0 || rank > n_peers)
         return fail(B200Q_EINVAL, "peer_barrier: needs the sync words of every rank and a valid rank");
-    B200Q_CUDA(cudaSetDevice(device));
+    B200Q_DEVICE(device);
     return launch_peer_barrier(sync_local, sync_peers, n_peers, rank, sync_local + 25, static_cast<cudaStream_t>(stream));
 }
 
@@ -463,7 +483,7 @@ int b200q_dense_f32_prefill_noalloc(b200q_weight_t h, const float *x_dev, int64_
     if (y_ld == 0) y_ld = w->n;
     if (y_ld < w->n) return fail(B200Q_EINVAL, "dense_noalloc: y_ld smaller than N");
     if (reinterpret_cast<uintptr_t>(x_dev) & 15) return fail(B200Q_EINVAL, "dense_noalloc: x must be 16-byte aligned");
-    B200Q_CUDA(cudaSetDevice(w->device));
+    B200Q_DEVICE(w->device);
     g_last_kernel = B200Q_KERNEL_GEMM_TCGEN05;
     return launch_gemm_f32_static(*w, x_dev, m, bias_dev, activation, y_dev, y_ld, static_cast<cudaStream_t>(stream));
 }
@@ -476,7 +496,7 @@ int b200q_embedding_lookup(b200q_weight_t h, const int32_t *idx_dev, int64_t n_i
     if (n_idx < 0) return fail(B200Q_EINVAL, "embedding_lookup: negative count");
     if (n_idx == 0) return B200Q_OK;
     if (!idx_dev || !out_dev) return fail(B200Q_EINVAL, "embedding_lookup: null pointer");
-    B200Q_CUDA(cudaSetDevice(w->device));
+    B200Q_DEVICE(w->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     int rc = launch_gather(*w, idx_dev, n_idx, out_dev, s);
     if (rc != 0) return rc;
@@ -492,7 +512,7 @@ int b200q_dense_host(b200q_weight_t h, const void *x_host, int x_dtype, int64_t 
     if (m < 0 || !x_host || !y_host) return fail(B200Q_EINVAL, "dense_host: bad arguments");
     if (m == 0) return B200Q_OK;
     if (x_dtype != B200Q_F32 && x_dtype != B200Q_BF16) return fail(B200Q_EINVAL, "dense_host: x dtype must be f32 or bf16");
-    B200Q_CUDA(cudaSetDevice(w->device));
+    B200Q_DEVICE(w->device);
     const size_t xb = (size_t)m * w->k * (x_dtype == B200Q_F32 ? 4 : 2), yb = (size_t)m * w->n * 4, bb = (size_t)w->n * 4;
     uint8_t *dev = nullptr;
     const size_t xo = 0, yo = (xb + 255) & ~(size_t)255, bo = yo + ((yb + 255) & ~(size_t)255);
@@ -519,7 +539,7 @@ int b200q_embedding_lookup_host(b200q_weight_t h, const int32_t *idx_host, int64
     if (n_idx < 0) return fail(B200Q_EINVAL, "embedding_lookup_host: negative count");
     if (n_idx == 0) return B200Q_OK;
     if (!idx_host || !out_host) return fail(B200Q_EINVAL, "embedding_lookup_host: null pointer");
-    B200Q_CUDA(cudaSetDevice(w->device));
+    B200Q_DEVICE(w->device);
     const size_t ib = ((size_t)n_idx * 4 + 255) & ~(size_t)255, ob = (size_t)n_idx * w->k * 4;
     uint8_t *dev = nullptr;
     B200Q_CUDA(cudaMalloc(&dev, ib + ob));
@@ -539,7 +559,7 @@ int b200q_dequantize_host(b200q_weight_t h, float *out_host) {
     auto w = find(h);
     if (!w) return fail(B200Q_EHANDLE, "dequantize_host: unknown handle");
     if (!out_host) return fail(B200Q_EINVAL, "dequantize_host: null output");
-    B200Q_CUDA(cudaSetDevice(w->device));
+    B200Q_DEVICE(w->device);
     float *dev = nullptr;
     const size_t ob = (size_t)w->n * w->k * 4;
     B200Q_CUDA(cudaMalloc(&dev, ob));
@@ -552,27 +572,27 @@ int b200q_dequantize_host(b200q_weight_t h, float *out_host) {
 
 int b200q_buffer_alloc(int device, size_t nbytes, void **dev_ptr) {
     if (!dev_ptr) return fail(B200Q_EINVAL, "buffer_alloc: null output");
-    B200Q_CUDA(cudaSetDevice(device));
+    B200Q_DEVICE(device);
     B200Q_CUDA(cudaMalloc(dev_ptr, nbytes ? nbytes : 1));
     return B200Q_OK;
 }
 int b200q_buffer_free(int device, void *dev_ptr) {
-    B200Q_CUDA(cudaSetDevice(device));
+    B200Q_DEVICE(device);
     B200Q_CUDA(cudaFree(dev_ptr));
     return B200Q_OK;
 }
 int b200q_buffer_h2d(int device, void *dst_dev, const void *src_host, size_t nbytes, void *stream) {
-    B200Q_CUDA(cudaSetDevice(device));
+    B200Q_DEVICE(device);
     B200Q_CUDA(cudaMemcpyAsync(dst_dev, src_host, nbytes, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
     return B200Q_OK;
 }
 int b200q_buffer_d2h(int device, void *dst_host, const void *src_dev, size_t nbytes, void *stream) {
-    B200Q_CUDA(cudaSetDevice(device));
+    B200Q_DEVICE(device);
     B200Q_CUDA(cudaMemcpyAsync(dst_host, src_dev, nbytes, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
     return B200Q_OK;
 }
 int b200q_stream_sync(int device, void *stream) {
-    B200Q_CUDA(cudaSetDevice(device));
+    B200Q_DEVICE(device);
     B200Q_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
     return B200Q_OK;
 }

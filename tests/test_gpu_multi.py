@@ -43,6 +43,11 @@ def _worker(rank, world, port, q):
         n2 = 512 + 16
         bufs = PeerScatterBuffers(max_m * (n + n2), rank)  # one symmetric allocation for both parts of the test
         stage("symmetric buffers")
+        # a call for another device leaves this thread's current device alone
+        other = g.upload(o.make_weights(o.Q8_0, 32, 256, seed=6), g.GGMLQuantType.Q8_0, (rank + 1) % world)
+        assert torch.cuda.current_device() == rank
+        other.free()
+        assert torch.cuda.current_device() == rank
         layer = PeerScatterDense(w, quant, bufs, 0, max_m, rank)
         bad = []  # numeric failures are reported after the last barrier, so that no rank waits for one that left
         for m in (1, 5):
